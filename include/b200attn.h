@@ -454,6 +454,43 @@ int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const void* gate
                     const float* weight, float eps, int32_t rows, int32_t n, int32_t groups,
                     int32_t gate_first, int32_t gate_act, int32_t dtype, b200_stream_t stream);
 
+/* out[i] = act(x[i]); act: 0 silu, 1 relu, 2 gelu (tanh form), 3 squared relu. */
+int b200_act_only(void* out, const void* x, int64_t total, int32_t act, int32_t dtype, b200_stream_t stream);
+
+/* A norm on a sublayer's OUTPUT, then the fp32 residual: u = y[iy] (+ y2[iy2]); n = norm(u) -- kind 0: layer norm
+ * (u - mean) / sqrt(var + eps) * w + b (b may be NULL), kind 1: u / sqrt(mean u^2 + eps) * (offset + w); residual
+ * <- accumulate ? residual + n : n; h (may be NULL) <- residual in `dtype`. iy = y_index ? clamp(y_index[r], y_rows)
+ * : r, likewise iy2: rows gathered by token id / position (embedding + learned position + norm in one launch). */
+int b200_norm_residual(void* h, float* residual, const void* y, const int64_t* y_index, int64_t y_rows,
+                       const void* y2, const int64_t* y2_index, int64_t y2_rows, const float* w, const float* b,
+                       float eps, float offset, int32_t kind, int32_t accumulate, int32_t rows, int32_t hidden,
+                       int32_t dtype, b200_stream_t stream);
+
+/* In place on x [T, nq | nk | nv] (row stride `stride`): q and k are divided by the root mean square of ALL their
+ * columns (every head at once) and multiplied by the plain weights wq [nq], wk [nk]; k and v rows are stored at
+ * `slots` of the paged caches [nb, bs, nk] / [nb, bs, nv] when those are given. nk == nv == 0: queries only. */
+int b200_rownorm_cache(void* x, int64_t stride, const float* wq, const float* wk, float eps, void* k_cache,
+                       void* v_cache, const int32_t* slots, int32_t slot_pairs, int32_t block_size,
+                       int32_t num_tokens, int32_t nq, int32_t nk, int32_t nv, int32_t dtype,
+                       b200_stream_t stream);
+
+/* q_out = silu(q), f_out = lower + (1 - lower) * sigmoid(f + bias), both fp32 [T, n]; q, f [T, n] views of the
+ * element type with row strides; bias, lower fp32 [n] or NULL (0). */
+int b200_gate_prep(float* q_out, float* f_out, const void* q, int64_t q_stride, const void* f, int64_t f_stride,
+                   const float* bias, const float* lower, int32_t num_tokens, int32_t n, int32_t dtype,
+                   b200_stream_t stream);
+
+/* Causal softmax attention whose heads are mixed BEFORE the softmax: s_h(i, j) = scale q_h,i.k_j - slopes[h] (i - j);
+ * s'_h = sum_g talk[h, g] s_g; softmax over the visible keys with exp(sink[h]) added to the denominator. slopes,
+ * talk, sink: fp32 or NULL (no bias / no mixing / no sink). Shapes, paging, spans and the window as in
+ * b200_attn_generic; vdim <= 256, num_heads <= 64 (32 above vdim 128). */
+int b200_mixed_attn(void* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                    int64_t v_stride, const int32_t* block_tables, int32_t bt_stride, int32_t block_size,
+                    const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens, int32_t num_seqs,
+                    int32_t max_q, int32_t num_heads, int32_t num_kv_heads, int32_t dim, int32_t vdim, float scale,
+                    int32_t window, const float* slopes, const float* talk, const float* sink, int32_t dtype,
+                    b200_stream_t stream);
+
 /* out[r, i] = act(x[r, i]) * x[r, inter + i]; act: 0 silu, 1 relu, 2 gelu (tanh form). */
 int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t inter, int32_t act, int32_t dtype,
                      b200_stream_t stream);
@@ -473,10 +510,12 @@ int b200_attn_generic(void* out, const void* q, int64_t q_stride, const void* k,
  * [slots, H, kdim, vdim]. q, k [T, groups*kdim] (head h reads group h / (H / groups)), v [T, H*vdim];
  * out fp32 [T, H*vdim]. mode 0: a_t = decay[h], b_t = 1, optional silu on q, k, v as read. mode 1:
  * step = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) step), b_t = step, o_t += d_skip[h] v_t.
+ * mode 2: `k` holds a forget gate f per key channel (fp32, as q: qk_f32 or an fp32 model) that also decides what is
+ * written, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; token by token.
  * max_q: the longest span of the step; bf16 prompt portions (max_q >= 16, kdim, vdim <= 128) run 16 tokens
  * at a time on the tensor cores with every fp32 operand split into three bf16 terms, everything else token
  * by token on the fp32 pipes. qk_f32: q and k are fp32 whatever the dtype (rotated or normalised upstream in
- * 32-bit; mode 0 only, token by token), v stays in dtype. */
+ * 32-bit; modes 0 and 2, token by token), v stays in dtype. */
 int b200_linear_recurrence(float* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
                            const void* v, int64_t v_stride, float* state, const int32_t* state_slots,
                            const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
@@ -559,8 +598,14 @@ int b200_moe_route_grouped(int32_t* topk_ids, float* topk_weights, const float* 
                            int64_t logit_stride, const float* bias, int32_t tokens, int32_t num_experts,
                            int32_t top_k, int32_t groups, int32_t keep, float scale, b200_stream_t stream);
 
-/* Expert GEMMs for any sizes and dtypes over the plan of b200_moe_align. gate_up: out [pairs, n_out] (dtype) =
- * silu(x Wg^T) * (x Wu^T), x rows gathered by sorted_pair / top_k, w [E, 2*n_out, K]. Otherwise: out
+/* The k largest of router_logits + bias (fp32 [tokens, E]); weights = softmax over the chosen logits only. */
+int b200_moe_route_topk(int32_t* topk_ids, float* topk_weights, const float* router_logits, int64_t logit_stride,
+                        const float* bias, int32_t tokens, int32_t num_experts, int32_t top_k,
+                        b200_stream_t stream);
+
+/* Expert GEMMs for any sizes and dtypes over the plan of b200_moe_align. gate_up == 1: out [pairs, n_out] (dtype) =
+ * silu(x Wg^T) * (x Wu^T), x rows gathered by sorted_pair / top_k, w [E, 2*n_out, K]. gate_up == 2 + act: out
+ * [pairs, n_out] (dtype) = act(x Wu^T) without a gate, w [E, n_out, K], act as in b200_act_only. gate_up == 0: out
  * [pairs, n_out] fp32 = a W^T with a [pairs, K] in plan order, w [E, n_out, K]. */
 int b200_moe_gemm_generic(void* out, const void* a, int64_t a_stride, const void* w, const int32_t* offsets,
                           const int32_t* sorted_pair, int32_t num_pairs, int32_t K, int32_t n_out,

@@ -6,7 +6,9 @@
 //                        group scores the sum of its two largest choices, only the `keep` best groups stay in
 //                        play (the others count as -inf); the top-k choices are taken and weighted by
 //                        s / (sum s + 1e-20) * scale. Ties go to the lower index. fp32 throughout.
+//   moe_route_topk       the k largest of z + bias; weights = softmax over the chosen logits only. fp32 throughout.
 //   moe_gemm_generic     H[pos] = silu(X[token(pos)] Wg[e]^T) * (X[token(pos)] Wu[e]^T)   (gate_up)
+//                        H[pos] = act(X[token(pos)] Wu[e]^T)                               (up alone, no gate)
 //                        Y[pos] = H[pos] W2[e]^T, fp32                                     (down)
 //                        over the dispatch plan of moe_align (pairs sorted by expert); 32 x 64 tiles, fp32 FMA.
 //   moe_combine_weighted out[t] = sum_j w[t][j] Y[pos(t, j)], accumulated in fp32, one rounding.
@@ -22,7 +24,7 @@ constexpr int kRouteMaxGroups = 64;
 __global__ void __launch_bounds__(128)
 moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits,
                          int64_t logit_stride, const float* __restrict__ bias, int tokens, int E, int top_k,
-                         int groups, int keep, float scale) {
+                         int groups, int keep, float scale, int kind) {
   extern __shared__ float smem[];                    // per warp: choice [E], s [E]
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -31,9 +33,15 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
   float* choice = smem + (size_t)warp * 2 * E;
   float* sg = choice + E;
   for (int e = lane; e < E; e += 32) {
-    const float s = sigmoid_f(logits[t * logit_stride + e]);
-    sg[e] = s;
-    choice[e] = s + (bias != nullptr ? bias[e] : 0.f);
+    if (kind == 1) {                                 // the bias is part of the logit; weights: softmax over the chosen
+      const float z = logits[t * logit_stride + e] + (bias != nullptr ? bias[e] : 0.f);
+      sg[e] = z;
+      choice[e] = z;
+    } else {
+      const float s = sigmoid_f(logits[t * logit_stride + e]);
+      sg[e] = s;
+      choice[e] = s + (bias != nullptr ? bias[e] : 0.f);
+    }
   }
   __syncwarp();
   if (groups > 1 && keep < groups) {
@@ -80,7 +88,7 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
     }
     __syncwarp();
   }
-  float wsum = 0.f, mine = 0.f;
+  float wsum = 0.f, mine = 0.f, zmax = 0.f;
   int my_id = 0;
   for (int j = 0; j < top_k; ++j) {
     float best = -INFINITY;
@@ -96,7 +104,11 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
       if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
     }
     if (arg >= E) arg = 0;                            // fewer candidates than top_k: cannot happen with keep*per >= top_k
-    const float s = sg[arg];
+    float s = sg[arg];
+    if (kind == 1) {                                 // the first pick is the largest logit
+      if (j == 0) zmax = s;
+      s = expf(s - zmax);
+    }
     wsum += s;
     if (lane == j) mine = s, my_id = arg;
     __syncwarp();
@@ -105,7 +117,7 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
   }
   if (lane < top_k) {
     ids[t * top_k + lane] = my_id;
-    weights[t * top_k + lane] = mine / (wsum + 1e-20f) * scale;
+    weights[t * top_k + lane] = kind == 1 ? mine / wsum : mine / (wsum + 1e-20f) * scale;
   }
 }
 
@@ -117,13 +129,27 @@ struct MoeGenericParams {
   const int32_t *offsets, *sorted_pair;
   int64_t a_stride;
   int K, n_out, top_k;
+  int act;                    // up alone: 0 silu, 1 relu, 2 gelu (tanh form), 3 squared relu
 };
+
+__device__ __forceinline__ float plain_act(float x, int act) {
+  if (act == 1) return fmaxf(x, 0.f);
+  if (act == 2) return gelu_tanh_f(x);
+  if (act == 3) {
+    const float r = fmaxf(x, 0.f);
+    return r * r;
+  }
+  return silu_f(x);
+}
 
 constexpr int kGM = 32, kGN = 64, kGK = 16;
 
-template <typename T, bool kGateUp>
+// kMode 0: down (fp32 out, rows in plan order); 1: silu(gate) * up; 2: act(up) alone (p.act: the codes of act_only)
+template <typename T, int kMode>
 __global__ void __launch_bounds__(256)
 moe_gemm_generic_kernel(const MoeGenericParams p) {
+  constexpr bool kGateUp = kMode == 1;
+  constexpr bool kGather = kMode != 0;
   __shared__ float sa[kGK][kGM + 1];
   __shared__ float sb[kGateUp ? 2 : 1][kGK][kGN + 1];
   __shared__ int srow[kGM];
@@ -139,7 +165,7 @@ moe_gemm_generic_kernel(const MoeGenericParams p) {
     __syncthreads();
     if (tid < kGM) {
       const int r = m0 + tid;
-      srow[tid] = r < cnt ? (kGateUp ? p.sorted_pair[row_begin + r] / p.top_k : row_begin + r) : -1;
+      srow[tid] = r < cnt ? (kGather ? p.sorted_pair[row_begin + r] / p.top_k : row_begin + r) : -1;
     }
     float acc[2][4], acc2[2][4];
 #pragma unroll
@@ -186,6 +212,7 @@ moe_gemm_generic_kernel(const MoeGenericParams p) {
         if (c >= p.n_out) continue;
         const int64_t o = (int64_t)(row_begin + r) * p.n_out + c;
         if (kGateUp) reinterpret_cast<T*>(p.out)[o] = from_f32<T>(silu_f(acc[i][j]) * acc2[i][j]);
+        else if (kMode == 2) reinterpret_cast<T*>(p.out)[o] = from_f32<T>(plain_act(acc[i][j], p.act));
         else reinterpret_cast<float*>(p.out)[o] = acc[i][j];
       }
     }
@@ -225,7 +252,20 @@ extern "C" int b200_moe_route_grouped(int32_t* topk_ids, float* topk_weights, co
   B200_RETURN_IF(!topk_ids || !topk_weights || !router_logits, B200_ERR_NULL_POINTER);
   const size_t smem = (size_t)4 * 2 * num_experts * sizeof(float);
   launch_pdl(moe_route_grouped_kernel, dim3((tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, topk_ids,
-             topk_weights, router_logits, logit_stride, bias, tokens, num_experts, top_k, groups, keep, scale);
+             topk_weights, router_logits, logit_stride, bias, tokens, num_experts, top_k, groups, keep, scale, 0);
+  return finish_launch();
+}
+
+extern "C" int b200_moe_route_topk(int32_t* topk_ids, float* topk_weights, const float* router_logits,
+                                   int64_t logit_stride, const float* bias, int32_t tokens, int32_t num_experts,
+                                   int32_t top_k, b200_stream_t stream) {
+  B200_RETURN_IF(tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts, B200_ERR_BAD_SHAPE);
+  B200_RETURN_IF(num_experts > kRouteMaxExperts || top_k > kRouteMaxTopK, B200_ERR_UNSUPPORTED);
+  if (tokens == 0) return B200_OK;
+  B200_RETURN_IF(!topk_ids || !topk_weights || !router_logits, B200_ERR_NULL_POINTER);
+  const size_t smem = (size_t)4 * 2 * num_experts * sizeof(float);
+  launch_pdl(moe_route_grouped_kernel, dim3((tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, topk_ids,
+             topk_weights, router_logits, logit_stride, bias, tokens, num_experts, top_k, 1, 1, 1.0f, 1);
   return finish_launch();
 }
 
@@ -237,13 +277,15 @@ extern "C" int b200_moe_gemm_generic(void* out, const void* a, int64_t a_stride,
   B200_RETURN_IF(num_local > 65535, B200_ERR_UNSUPPORTED);
   if (num_pairs == 0) return B200_OK;
   B200_RETURN_IF(!out || !a || !w || !offsets || !sorted_pair, B200_ERR_NULL_POINTER);
-  MoeGenericParams p{a, w, out, offsets, sorted_pair, a_stride, K, n_out, top_k};
+  B200_RETURN_IF(gate_up < 0 || gate_up > 5, B200_ERR_BAD_SHAPE);
+  MoeGenericParams p{a, w, out, offsets, sorted_pair, a_stride, K, n_out, top_k, gate_up >= 2 ? gate_up - 2 : 0};
   int my = (num_pairs + kGM - 1) / kGM;
   if (my > 32) my = 32;
   const dim3 grid((n_out + kGN - 1) / kGN, my, num_local);
   B200_DISPATCH_3(dtype, T, {
-    if (gate_up) launch_pdl(moe_gemm_generic_kernel<T, true>, grid, dim3(256), 0, (cudaStream_t)stream, p);
-    else launch_pdl(moe_gemm_generic_kernel<T, false>, grid, dim3(256), 0, (cudaStream_t)stream, p);
+    if (gate_up == 1) launch_pdl(moe_gemm_generic_kernel<T, 1>, grid, dim3(256), 0, (cudaStream_t)stream, p);
+    else if (gate_up >= 2) launch_pdl(moe_gemm_generic_kernel<T, 2>, grid, dim3(256), 0, (cudaStream_t)stream, p);
+    else launch_pdl(moe_gemm_generic_kernel<T, 0>, grid, dim3(256), 0, (cudaStream_t)stream, p);
   });
   return finish_launch();
 }

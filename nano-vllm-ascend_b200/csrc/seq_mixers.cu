@@ -5,8 +5,10 @@
 //                      prompt portions and single tokens in one launch. fp32 scores, softmax and accumulation.
 //   linear_recurrence  S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t (+ d v_t) per head with the state S
 //                      [key size x value size] held in fp32 registers and carried between steps in a slot.
-//                      Two forms: a constant decay per head (lightning attention), or a decay and a step size
-//                      computed per token from a projected dt (the selective state-space form of Mamba-2).
+//                      Three forms: a constant decay per head (lightning attention), a decay and a step size
+//                      computed per token from a projected dt (the selective state-space form of Mamba-2), or a
+//                      forget gate per key channel that also decides what is written (k = 1 - f: the tied form
+//                      of HGRN2), S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T.
 #include "seq_common.cuh"
 
 namespace b200 {
@@ -138,7 +140,8 @@ struct RecParams {
   float* state;                     // [slots, H, kdim, vdim] fp32 or nullptr (start from zero, keep nothing)
   const int *state_slots, *cu_q, *cu_k, *ctx_lens;
   int H, groups, kdim, vdim;
-  int mode;                         // 0: constant decay per head; 1: selective (dt)
+  int mode;                         // 0: constant decay per head; 1: selective (dt); 2: `k` holds a forget gate f per
+                                    //    key channel (fp32): S <- diag(f) S + (1 - f) v^T
   int act_silu;                     // silu on q, k, v as they are read (mode 0)
   const float* decay;               // mode 0: [H]
   const void* dt;                   // mode 1: [tokens, H] element type T, before bias and softplus
@@ -267,6 +270,20 @@ linear_recurrence_kernel(const RecParams P) {
       const float4* q4 = reinterpret_cast<const float4*>(sq + tt * KP + ksl * KS);
       const float4* k4 = reinterpret_cast<const float4*>(skk + tt * KP + ksl * KS);
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      if (P.mode == 2) {                             // f S + (1 - f) v = v + f (S - v): the gate is the staged `k`
+#pragma unroll
+        for (int r4 = 0; r4 < KPT / 4; ++r4) {
+          const float4 f4 = k4[r4], qq = q4[r4];
+          S[r4 * 4 + 0] = fmaf(f4.x, S[r4 * 4 + 0] - vj, vj);
+          o0 += S[r4 * 4 + 0] * qq.x;
+          S[r4 * 4 + 1] = fmaf(f4.y, S[r4 * 4 + 1] - vj, vj);
+          o1 += S[r4 * 4 + 1] * qq.y;
+          S[r4 * 4 + 2] = fmaf(f4.z, S[r4 * 4 + 2] - vj, vj);
+          o2 += S[r4 * 4 + 2] * qq.z;
+          S[r4 * 4 + 3] = fmaf(f4.w, S[r4 * 4 + 3] - vj, vj);
+          o3 += S[r4 * 4 + 3] * qq.w;
+        }
+      } else {
 #pragma unroll
       for (int r4 = 0; r4 < KPT / 4; ++r4) {
         const float4 kq = k4[r4], qq = q4[r4];
@@ -278,6 +295,7 @@ linear_recurrence_kernel(const RecParams P) {
         o2 += S[r4 * 4 + 2] * qq.z;
         S[r4 * 4 + 3] = a * S[r4 * 4 + 3] + kq.w * vj;
         o3 += S[r4 * 4 + 3] * qq.w;
+      }
       }
       float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
@@ -595,7 +613,7 @@ static bool chunk_recurrence_ok(const RecParams& P, int dtype, int max_q) {
     const char* e = getenv("B200_CHUNK_RECURRENCE");
     return e != nullptr && e[0] == '0';
   }();
-  return !off && dtype == B200_DTYPE_BF16 && P.cu_q != nullptr && max_q >= kChunk && P.kdim <= 128 && P.vdim <= 128;
+  return !off && P.mode != 2 && dtype == B200_DTYPE_BF16 && P.cu_q != nullptr && max_q >= kChunk && P.kdim <= 128 && P.vdim <= 128;
 }
 
 static int chunk_recurrence_launch(const RecParams& P, int num_seqs, cudaStream_t stream) {
@@ -667,19 +685,20 @@ extern "C" int b200_linear_recurrence(float* out, const void* q, int64_t q_strid
                                       const float* dt_bias, const float* a_log, const float* d_skip,
                                       int32_t qk_f32, int32_t dtype, b200_stream_t stream) {
   B200_RETURN_IF(num_seqs < 0 || num_heads <= 0 || groups <= 0 || num_heads % groups != 0 || kdim <= 0 ||
-                     vdim <= 0 || (mode != 0 && mode != 1), B200_ERR_BAD_SHAPE);
+                     vdim <= 0 || mode < 0 || mode > 2, B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(kdim > 256, B200_ERR_UNSUPPORTED);
   if (num_seqs == 0) return B200_OK;
   B200_RETURN_IF(!out || !q || !k || !v || (cu_q == nullptr) == (ctx_lens == nullptr) || (cu_q && !cu_k) ||
                      (state && !state_slots), B200_ERR_NULL_POINTER);
-  B200_RETURN_IF(mode == 0 ? !decay : (!dt || !dt_bias || !a_log || !d_skip), B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(mode == 0 ? !decay : (mode == 1 && (!dt || !dt_bias || !a_log || !d_skip)), B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(mode == 2 && !qk_f32 && dtype != B200_DTYPE_F32, B200_ERR_BAD_DTYPE);   // the gate is fp32
   RecParams P;
   P.q = q, P.k = k, P.v = v, P.q_stride = q_stride, P.k_stride = k_stride, P.v_stride = v_stride;
   P.out = out, P.state = state, P.state_slots = state_slots, P.cu_q = cu_q, P.cu_k = cu_k, P.ctx_lens = ctx_lens;
   P.H = num_heads, P.groups = groups, P.kdim = kdim, P.vdim = vdim, P.mode = mode, P.act_silu = act_silu;
   P.decay = decay, P.dt = dt, P.dt_stride = dt_stride, P.dt_bias = dt_bias, P.a_log = a_log, P.d_skip = d_skip;
   if (qk_f32 && dtype != B200_DTYPE_F32) {           // q, k already fp32 (rotated or normalised upstream), v as projected
-    B200_RETURN_IF(mode != 0, B200_ERR_UNSUPPORTED);
+    B200_RETURN_IF(mode == 1, B200_ERR_UNSUPPORTED);
     if (dtype == B200_DTYPE_BF16) return recurrence_launch<float, __nv_bfloat16>(P, num_seqs, (cudaStream_t)stream);
     if (dtype == B200_DTYPE_F16) return recurrence_launch<float, __half>(P, num_seqs, (cudaStream_t)stream);
     return B200_ERR_BAD_DTYPE;

@@ -6,6 +6,13 @@
 //   unitnorm_temp_cache  per-head unit RMS of q and k, position-dependent query temperature, K/V scatter
 //   gated_norm           (grouped) RMS norm and an output gate, in either order
 //   act_and_mul          act(gate) * up for the gated feed-forward
+//   act_only             act(x) for a feed-forward without a gate (silu, relu, gelu, squared relu)
+//   norm_residual        r (+)= norm(y [+ y2]); h = r in the element type: a norm on the sublayer's OUTPUT (layer norm
+//                        with weight and bias, or RMS norm), the rows of y / y2 optionally gathered by index
+//                        (token embedding + learned position + norm in one launch)
+//   rownorm_cache        RMS norm of q and of k over the WHOLE projection (all heads at once), K/V scatter
+//   gate_prep            what a gated linear recurrence with tied input reads: silu(q) and the lower-bounded forget
+//                        gate l + (1 - l) sigmoid(f + bias), both fp32
 //
 // All are bound by HBM traffic; arithmetic is fp32 whatever the element type. Shapes are free: no
 // multiple-of-8 rule, so that small and odd models run (a 16-byte path is taken where rows allow it).
@@ -368,7 +375,7 @@ unitnorm_temp_cache_vec_kernel(T* __restrict__ qkv, int64_t stride, const int64_
 // y: [rows, n] fp32 or T; gate: [rows, n] T with a row stride. One CTA per (row, group of n / groups):
 //   gate_first: out = norm_group(y * act(gate)) * w          (gate, then norm)
 //   else      : out = norm_group(y) * w * act(gate)          (norm, then gate)
-// w == nullptr: no norm at all, out = y * act(gate). gate_act: 0 sigmoid, 1 silu.
+// w == nullptr: no norm at all, out = y * act(gate). gate_act: 0 sigmoid, 1 silu, 2 no gate (gate may be null).
 template <typename T, typename Y>
 __global__ void __launch_bounds__(256)
 gated_norm_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __restrict__ gate,
@@ -382,6 +389,7 @@ gated_norm_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __restr
   const T* gr = gate + r * gate_stride + lo;
   T* o = out + r * n + lo;
   auto gate_at = [&](int i) -> float {
+    if (gate_act == 2) return 1.f;
     const float g = to_f32<T>(gr[i]);
     return gate_act == 1 ? silu_f(g) : sigmoid_f(g);
   };
@@ -461,10 +469,10 @@ gated_norm_vec_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __r
     const int vi = threadIdx.x + m * blockDim.x;
     if (vi * 8 < len) {
       load8<Y>(yr + vi * 8, val[m]);
-      load8<T>(gr + vi * 8, gv[m]);
+      if (gate_act != 2) load8<T>(gr + vi * 8, gv[m]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        gv[m][e] = gate_act == 1 ? silu_f(gv[m][e]) : sigmoid_f(gv[m][e]);
+        gv[m][e] = gate_act == 2 ? 1.f : gate_act == 1 ? silu_f(gv[m][e]) : sigmoid_f(gv[m][e]);
         if (gate_first || w == nullptr) val[m][e] *= gv[m][e];
         ss += val[m][e] * val[m][e];
       }
@@ -517,10 +525,10 @@ gated_norm_warp_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __
     const int vi = sub + m * gl;
     if (live && vi * 8 < len && (m == 0 || gl == 32)) {
       load8<Y>(yr + vi * 8, val[m]);
-      load8<T>(gr + vi * 8, gv[m]);
+      if (gate_act != 2) load8<T>(gr + vi * 8, gv[m]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        gv[m][e] = gate_act == 1 ? silu_f(gv[m][e]) : sigmoid_f(gv[m][e]);
+        gv[m][e] = gate_act == 2 ? 1.f : gate_act == 1 ? silu_f(gv[m][e]) : sigmoid_f(gv[m][e]);
         if (gate_first) val[m][e] *= gv[m][e];
         ss += val[m][e] * val[m][e];
       }
@@ -538,6 +546,151 @@ gated_norm_warp_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __
       for (int e = 0; e < 8; ++e) ov[e] = gate_first ? val[m][e] * rstd * wv[e] : val[m][e] * rstd * wv[e] * gv[m][e];
       store8<T>(o + vi * 8, ov);
     }
+  }
+}
+
+// ------------------------------------------------------------------ act(x) without a gate
+// act: 0 silu, 1 relu, 2 gelu (tanh form), 3 squared relu.
+__device__ __forceinline__ float act_f(float x, int act) {
+  if (act == 1) return fmaxf(x, 0.f);
+  if (act == 2) return gelu_tanh_f(x);
+  if (act == 3) {
+    const float r = fmaxf(x, 0.f);
+    return r * r;
+  }
+  return silu_f(x);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_only_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t total, int act) {
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(act_f(to_f32<T>(x[i]), act));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_only_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t total8, int act) {
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    load8<T>(x + i * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = act_f(v[e], act);
+    store8<T>(out + i * 8, v);
+  }
+}
+
+// ------------------------------------------------------------------ a norm on the sublayer's output, then the residual
+// u = y[iy] (+ y2[iy2]) in fp32; n = norm(u): kind 0 (u - mean) / sqrt(var + eps) * w + b, kind 1 u / sqrt(mean u^2 + eps)
+// * (offset + w); r <- accumulate ? r + n : n; h <- r in the element type (h may be null). iy / iy2: row r itself, or
+// index[r] clamped to the table's rows (a token id, a position). Dynamic smem: hidden floats.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_residual_kernel(T* __restrict__ h, float* __restrict__ res, const T* __restrict__ y,
+                     const int64_t* __restrict__ y_index, int64_t y_rows, const T* __restrict__ y2,
+                     const int64_t* __restrict__ y2_index, int64_t y2_rows, const float* __restrict__ w,
+                     const float* __restrict__ b, float eps, float offset, int kind, int accumulate, int hidden) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  int64_t iy = y_index != nullptr ? y_index[r] : r;
+  if (y_index != nullptr) iy = iy < 0 ? 0 : (iy >= y_rows ? y_rows - 1 : iy);
+  const T* yr = y + iy * hidden;
+  const T* y2r = nullptr;
+  if (y2 != nullptr) {
+    int64_t i2 = y2_index != nullptr ? y2_index[r] : r;
+    if (y2_index != nullptr) i2 = i2 < 0 ? 0 : (i2 >= y2_rows ? y2_rows - 1 : i2);
+    y2r = y2 + i2 * hidden;
+  }
+  float s1 = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = to_f32<T>(yr[i]);
+    if (y2r != nullptr) v += to_f32<T>(y2r[i]);
+    row[i] = v;
+    s1 += kind == 0 ? v : v * v;
+  }
+  s1 = cta_sum(s1, red) / (float)hidden;
+  float mean = 0.f, rstd;
+  if (kind == 0) {
+    mean = s1;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = row[i] - mean;
+      sq += d * d;
+    }
+    rstd = 1.0f / sqrtf(cta_sum(sq, red) / (float)hidden + eps);
+  } else {
+    rstd = 1.0f / sqrtf(s1 + eps);
+  }
+  float* rr = res + r * hidden;
+  T* hr = h != nullptr ? h + r * hidden : nullptr;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float n = kind == 0 ? (row[i] - mean) * rstd * w[i] + (b != nullptr ? b[i] : 0.f) : row[i] * rstd * (offset + w[i]);
+    if (accumulate) n += rr[i];
+    rr[i] = n;
+    if (hr != nullptr) hr[i] = from_f32<T>(n);
+  }
+}
+
+// ------------------------------------------------------------------ q / k RMS norm over the whole projection + K/V scatter
+// One CTA per (token, part): part 0 = the nq query columns, 1 = the nk key columns, 2 = the nv value columns of row
+// x [nq | nk | nv]. q and k are divided by the root mean square of ALL their columns (every head at once), times a
+// plain weight, in place; k and v rows go to the paged caches at the token's slot (slot < 0: not stored).
+template <typename T>
+__global__ void __launch_bounds__(128)
+rownorm_cache_kernel(T* __restrict__ x, int64_t stride, const float* __restrict__ wq, const float* __restrict__ wk,
+                     float eps, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
+                     int slot_pairs, int block_size, int nq, int nk, int nv) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int part = blockIdx.y;
+  int64_t slot = -1;
+  if (k_cache != nullptr && part > 0)
+    slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+  T* row = x + t * stride;
+  if (part == 2) {
+    if (slot < 0) return;
+    const T* src = row + nq + nk;
+    T* dst = v_cache + slot * nv;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) dst[i] = src[i];
+    return;
+  }
+  const int n = part == 0 ? nq : nk;
+  T* p = row + (part == 0 ? 0 : nq);
+  const float* w = part == 0 ? wq : wk;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = to_f32<T>(p[i]);
+    ss += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)n + eps);
+  T* dst = (part == 1 && slot >= 0) ? k_cache + slot * nk : nullptr;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const T v = from_f32<T>(to_f32<T>(p[i]) * rstd * w[i]);
+    p[i] = v;
+    if (dst != nullptr) dst[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------ inputs of a gated recurrence with tied input
+// q32 = silu(q), f32 = l + (1 - l) sigmoid(f + bias): the gate and everything derived from it stay in 32-bit
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_prep_kernel(float* __restrict__ q_out, float* __restrict__ f_out, const T* __restrict__ q, int64_t q_stride,
+                 const T* __restrict__ f, int64_t f_stride, const float* __restrict__ bias,
+                 const float* __restrict__ lower, int64_t tokens, int n) {
+  pdl_wait();
+  const int64_t total = tokens * n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / n;
+    const int c = (int)(i - t * n);
+    q_out[i] = silu_f(to_f32<T>(q[t * q_stride + c]));
+    const float l = lower != nullptr ? lower[c] : 0.f;
+    f_out[i] = l + (1.0f - l) * sigmoid_f(to_f32<T>(f[t * f_stride + c]) + (bias != nullptr ? bias[c] : 0.f));
   }
 }
 
@@ -653,12 +806,13 @@ extern "C" int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const
                                b200_stream_t stream) {
   B200_RETURN_IF(rows < 0 || n <= 0 || groups <= 0 || n % groups != 0, B200_ERR_BAD_SHAPE);
   if (rows == 0) return B200_OK;
-  B200_RETURN_IF(!out || !y || !gate, B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(gate_act < 0 || gate_act > 2, B200_ERR_BAD_SHAPE);
+  B200_RETURN_IF(!out || !y || (!gate && gate_act != 2), B200_ERR_NULL_POINTER);
   const dim3 grid(rows, weight ? groups : 1);
   const int g = weight ? groups : 1;
   const int len = n / g;
   if (len % 8 == 0 && len <= 4096 && n % 8 == 0 && gate_stride % 8 == 0 && aligned16(out) && aligned16(y) &&
-      aligned16(gate) && (!weight || aligned16(weight))) {
+      (!gate || aligned16(gate)) && (!weight || aligned16(weight))) {
     if (weight && g > 1 && len <= 512) {               // a norm per head: warps, not CTAs, per group
       int gl = 1;
       while (gl * 8 < len && gl < 32) gl <<= 1;
@@ -714,5 +868,75 @@ extern "C" int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t 
   if (grid > 148 * 16) grid = 148 * 16;
   B200_DISPATCH_3(dtype, T, launch_pdl(act_and_mul_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
                                        (T*)out, (const T*)x, (int64_t)rows, inter, act));
+  return finish_launch();
+}
+
+extern "C" int b200_act_only(void* out, const void* x, int64_t total, int32_t act, int32_t dtype,
+                             b200_stream_t stream) {
+  B200_RETURN_IF(total < 0 || act < 0 || act > 3, B200_ERR_BAD_SHAPE);
+  if (total == 0) return B200_OK;
+  B200_RETURN_IF(!out || !x, B200_ERR_NULL_POINTER);
+  if (total % 8 == 0 && aligned16(out) && aligned16(x)) {
+    int vgrid = (int)((total / 8 + 255) / 256);
+    if (vgrid > 148 * 16) vgrid = 148 * 16;
+    B200_DISPATCH_3(dtype, T, launch_pdl(act_only_vec_kernel<T>, dim3(vgrid), dim3(256), 0, (cudaStream_t)stream,
+                                         (T*)out, (const T*)x, total / 8, act));
+    return finish_launch();
+  }
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  B200_DISPATCH_3(dtype, T, launch_pdl(act_only_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                                       (const T*)x, total, act));
+  return finish_launch();
+}
+
+extern "C" int b200_norm_residual(void* h, float* residual, const void* y, const int64_t* y_index, int64_t y_rows,
+                                  const void* y2, const int64_t* y2_index, int64_t y2_rows, const float* w,
+                                  const float* b, float eps, float offset, int32_t kind, int32_t accumulate,
+                                  int32_t rows, int32_t hidden, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || hidden <= 0 || (kind != 0 && kind != 1), B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!residual || !y || !w, B200_ERR_NULL_POINTER);
+  B200_RETURN_IF((y_index && y_rows <= 0) || (y2 && y2_index && y2_rows <= 0), B200_ERR_BAD_SHAPE);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
+  B200_DISPATCH_3(dtype, T, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_residual_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(norm_residual_kernel<T>, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (T*)h, residual,
+               (const T*)y, y_index, y_rows, (const T*)y2, y2_index, y2_rows, w, b, eps, offset, kind, accumulate,
+               hidden);
+  });
+  return finish_launch();
+}
+
+extern "C" int b200_rownorm_cache(void* x, int64_t stride, const float* wq, const float* wk, float eps,
+                                  void* k_cache, void* v_cache, const int32_t* slots, int32_t slot_pairs,
+                                  int32_t block_size, int32_t num_tokens, int32_t nq, int32_t nk, int32_t nv,
+                                  int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(num_tokens < 0 || nq <= 0 || nk < 0 || nv < 0, B200_ERR_BAD_SHAPE);
+  if (num_tokens == 0) return B200_OK;
+  B200_RETURN_IF(!x || !wq || (nk > 0 && !wk) || (k_cache == nullptr) != (v_cache == nullptr) || (k_cache && !slots),
+                 B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(k_cache && (nk <= 0 || nv <= 0), B200_ERR_BAD_SHAPE);
+  const dim3 grid(num_tokens, nk > 0 ? (k_cache ? 3 : 2) : 1);
+  B200_DISPATCH_3(dtype, T, launch_pdl(rownorm_cache_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, (T*)x,
+                                       stride, wq, wk, eps, (T*)k_cache, (T*)v_cache, slots, slot_pairs, block_size,
+                                       nq, nk, nv));
+  return finish_launch();
+}
+
+extern "C" int b200_gate_prep(float* q_out, float* f_out, const void* q, int64_t q_stride, const void* f,
+                              int64_t f_stride, const float* bias, const float* lower, int32_t num_tokens,
+                              int32_t n, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(num_tokens < 0 || n <= 0, B200_ERR_BAD_SHAPE);
+  if (num_tokens == 0) return B200_OK;
+  B200_RETURN_IF(!q_out || !f_out || !q || !f, B200_ERR_NULL_POINTER);
+  const int64_t total = (int64_t)num_tokens * n;
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  B200_DISPATCH_3(dtype, T, launch_pdl(gate_prep_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, q_out,
+                                       f_out, (const T*)q, q_stride, (const T*)f, f_stride, bias, lower,
+                                       (int64_t)num_tokens, n));
   return finish_launch();
 }

@@ -142,6 +142,20 @@ PROTOTYPES = {
     "b200_glu_clamped": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_float, c_float, c_int32, c_void_p]),
     "b200_moe_route_grouped": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_float, c_void_p]),
+    "b200_moe_route_topk": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_int32, c_int32,
+                                      c_void_p]),
+    "b200_act_only": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
+    "b200_norm_residual": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                     c_void_p, c_void_p, c_float, c_float, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                     c_void_p]),
+    "b200_rownorm_cache": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                     c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "b200_gate_prep": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int32,
+                                 c_int32, c_int32, c_void_p]),
+    "b200_mixed_attn": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                  c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                  c_int32, c_int32, c_int32, c_float, c_int32, c_void_p, c_void_p, c_void_p, c_int32,
+                                  c_void_p]),
     "b200_moe_gemm_generic": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32,
                                         c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200_moe_combine_weighted": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,

@@ -28,7 +28,8 @@ class NativeConfig:
         self.architectures = [data["architecture"]]
         self.dtype = data.get("dtype", "bfloat16")
         self.eos_token_id = data.get("eos_token_id", -1)
-        self.max_position_embeddings = data.get("max_position_embeddings")
+        # models with a learned position table name its length "max_positions": no sequence may grow past it
+        self.max_position_embeddings = data.get("max_position_embeddings", data.get("max_positions"))
 
     def to_dict(self) -> dict:
         return dict(self._data)
@@ -90,6 +91,35 @@ def nirelix_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, h
             "layers": [entry[ch] for ch in pattern] * repeats}
 
 
+def fitevik_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, head_dim: int = 128,
+                   window: int = 512, max_positions: int = 8192) -> dict:
+    """A Fitevik configuration of realistic layer sizes for synthetic benchmarks: `pattern` is a string over
+    h (hgrn2 + dense feed-forward), g (hgrn2 + mixture of experts), a (attention + dense feed-forward) and
+    b (attention that borrows the keys and values of the nearest earlier `a` layer, + mixture of experts), repeated
+    `repeats` times."""
+    H = width // head_dim
+    kv = max(1, H // 4)
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 2}}
+    rec = {"heads": H, "dim": head_dim, "vdim": head_dim}
+    att = {"heads": H, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "mask": {"size": window},
+           "scale": head_dim ** -0.5 * 8.0}
+    layers = []
+    for _ in range(repeats):
+        for ch in pattern:
+            if ch in "hg":
+                layers.append({"type": "hgrn2", "mixer": dict(rec), "mlp": dense if ch == "h" else moe})
+            elif ch == "a":
+                layers.append({"type": "attention", "mixer": dict(att), "mlp": dense})
+            elif ch == "b":
+                src = max(i for i, e in enumerate(layers) if e["type"] == "attention" and "kv_from" not in e["mixer"])
+                layers.append({"type": "attention", "mixer": dict(att, kv_from=src), "mlp": moe})
+            else:
+                raise ValueError(f"unknown layer letter {ch!r}")
+    return {"architecture": "Fitevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+            "max_positions": max_positions, "layers": layers}
+
+
 def preset_hf_config(name: str):
     """Architecture presets built offline from the public model cards."""
     from transformers import LlamaConfig, Qwen3Config, Qwen3MoeConfig
@@ -106,6 +136,12 @@ def preset_hf_config(name: str):
         return NativeConfig(nirelix_preset(2048, "rdad", 4, vocab=128256, head_dim=64))
     if key == "tiny-nirelix":
         return NativeConfig(nirelix_preset(128, "rda", 1, vocab=512, head_dim=32, streams=2, window=24))
+    if key == "fitevik-1k":          # 28 layers at width 1024: the size class of nirelix-1k, zegopel-1k and qwen3-0.6b
+        return NativeConfig(fitevik_preset(1024, "hgabhga", 4, vocab=151936))
+    if key == "fitevik-2k":          # 16 layers at width 2048, head size 64: the size class of nirelix-2k
+        return NativeConfig(fitevik_preset(2048, "hgab", 4, vocab=128256, head_dim=64))
+    if key == "tiny-fitevik":
+        return NativeConfig(fitevik_preset(128, "hgab", 1, vocab=512, head_dim=32, window=24, max_positions=512))
     if key == "qwen3-0.6b":
         c = Qwen3Config(vocab_size=151936, hidden_size=1024, num_hidden_layers=28,
                         num_attention_heads=16, num_key_value_heads=8, head_dim=128,

@@ -307,6 +307,10 @@ class ModelRunner:
             m.v_cache = self.kv_cache[off:off + nb * bs * v_row].view(nb, bs, v_row)
             off += nb * bs * v_row
             m.layer_id = layer
+        for m in attn_modules:                       # a layer that attends over another layer's keys and values
+            lender = getattr(m, "kv_source", None)
+            if lender is not None:
+                m.k_cache, m.v_cache = lender.k_cache, lender.v_cache
 
     # ------------------------------------------------------------------ prefill metadata
     def prepare_prefill(self, seqs: list[Sequence]):

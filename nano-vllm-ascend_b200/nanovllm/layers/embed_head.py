@@ -43,10 +43,14 @@ class ParallelLMHead(VocabParallelEmbedding):
     """Logits for the last token of every sequence (prefill) / every row (decode); with TP the
     vocab shards are gathered on rank 0, which is the only rank that samples."""
 
-    def __init__(self, num_embeddings: int, embedding_dim: int, bias: bool = False):
+    def __init__(self, num_embeddings: int, embedding_dim: int, bias: bool = False, scale: float = 1.0):
         if bias:
             raise ValueError("lm_head bias is not part of the reference path")
         super().__init__(num_embeddings, embedding_dim)
+        self.scale = float(scale)                   # logits = scale * (W x), for models that fix one
+
+    def _scaled(self, logits):
+        return logits if self.scale == 1.0 else logits * self.scale
 
     def local_logits(self, x):
         """This rank's vocabulary shard of the logits, no collective (the sharded sampling tail,
@@ -54,19 +58,19 @@ class ParallelLMHead(VocabParallelEmbedding):
         context = get_context()
         if context.is_prefill:
             x = x[(context.cu_seqlens_q[1:] - 1).long()].contiguous()
-        return F.linear(x, self.weight)
+        return self._scaled(F.linear(x, self.weight))
 
     def logits_at(self, x, rows):
         """Logits of the given rows of the step's hidden states (scoring: any position, not only the last)."""
         if self.tp_size > 1:
             raise NotImplementedError("logits at arbitrary rows are computed on one GPU")
-        return F.linear(x[rows].contiguous(), self.weight)
+        return self._scaled(F.linear(x[rows].contiguous(), self.weight))
 
     def forward(self, x):
         context = get_context()
         if context.is_prefill:
             x = x[(context.cu_seqlens_q[1:] - 1).long()].contiguous()
-        logits = F.linear(x, self.weight)
+        logits = self._scaled(F.linear(x, self.weight))
         if self.tp_size > 1 and tp_collectives():
             parts = [torch.empty_like(logits) for _ in range(self.tp_size)] if self.tp_rank == 0 else None
             dist.gather(logits, parts, 0)

@@ -1,8 +1,10 @@
 """Building blocks of hybrid decoders: a short causal convolution with a carried tail, linear recurrences
-with an fp32 state (constant decay per head, the selective state-space form, or the gated delta rule with a decay
-per key channel), the gated norms that follow them, rotary positions on part of a head, causal softmax attention
-whose key and value sizes may differ (optionally inside a sliding window), attention over a cached latent, and the
-mixing weights of a residual that is kept in several streams.
+with an fp32 state (constant decay per head, the selective state-space form, a forget gate per key channel that also
+decides what is written, or the gated delta rule with a decay per key channel), the gated norms that follow them,
+rotary positions on part of a head, causal softmax attention whose key and value sizes may differ (optionally inside
+a sliding window), attention whose heads are mixed before the softmax (with a distance bias, a sink, and keys and
+values that may be another layer's), attention over a cached latent, and the mixing weights of a residual that is
+kept in several streams.
 
 Every block reads the step's ``Context`` (which tokens belong to which sequence, their cache slots and
 state slots) and runs on the kernels of ``csrc/seq_ops.cu`` / ``csrc/seq_mixers.cu``. Per-sequence state is
@@ -66,14 +68,23 @@ class ShortConv(nn.Module):
 
 class LinearRecurrence(nn.Module):
     """o_t = S_t^T q_t with S_t = a_t S_(t-1) + k_t (b_t v_t)^T per head, S fp32 [kdim, vdim] in ``state``.
-    ``decay`` (a list, one constant per head) selects the constant-decay form; otherwise the selective form
-    with learned ``dt_bias``, ``A_log`` and ``D`` (a_t = exp(-exp(A_log) softplus(dt_t + dt_bias)))."""
+    ``decay`` (a list, one constant per head) selects the constant-decay form; ``tied_gate`` the form in which a forget
+    gate per key channel also decides what is written, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T with f = lower +
+    (1 - lower) sigmoid(W_f h + gate_bias) and q = silu(W_q h) (``forward(q, f, v)`` takes the raw projections; gate and
+    query are made fp32 by ops.gate_prep); otherwise the selective form with learned ``dt_bias``, ``A_log`` and ``D``
+    (a_t = exp(-exp(A_log) softplus(dt_t + dt_bias)))."""
 
-    def __init__(self, num_heads: int, groups: int, kdim: int, vdim: int, decay=None, act_silu: bool = False):
+    def __init__(self, num_heads: int, groups: int, kdim: int, vdim: int, decay=None, act_silu: bool = False,
+                 tied_gate: bool = False):
         super().__init__()
         self.num_heads, self.groups, self.kdim, self.vdim = num_heads, groups, kdim, vdim
         self.act_silu = act_silu
-        if decay is not None:
+        self.tied_gate = bool(tied_gate)
+        if tied_gate:
+            assert decay is None and not act_silu, "the tied-gate form has neither a constant decay nor an activation flag"
+            self.decay = None
+            self.lower, self.gate_bias = small_param(groups * kdim), small_param(groups * kdim)
+        elif decay is not None:
             self.register_buffer("decay", torch.tensor([float(d) for d in decay], dtype=F32), persistent=False)
             assert self.decay.numel() == num_heads, "one decay per head"
         else:
@@ -87,8 +98,13 @@ class LinearRecurrence(nn.Module):
     def forward(self, q, k, v, dt=None) -> torch.Tensor:
         """q and k may be fp32 beside 16-bit v (constant-decay form): rotated or normalised in 32-bit upstream."""
         ctx, spans, bound = _spans_and_slots(self.state)
-        kw = dict(decay=self.decay, act_silu=self.act_silu) if self.decay is not None else dict(
-            dt=dt, dt_bias=self.dt_bias, a_log=self.A_log, d_skip=self.D)
+        if self.tied_gate:
+            q, k = ops.gate_prep(q, k, self.gate_bias, self.lower)
+            kw = dict(tied_gate=True)
+        elif self.decay is not None:
+            kw = dict(decay=self.decay, act_silu=self.act_silu)
+        else:
+            kw = dict(dt=dt, dt_bias=self.dt_bias, a_log=self.A_log, d_skip=self.D)
         return ops.linear_recurrence(q, k, v, spans, self.num_heads, self.groups, self.kdim, self.vdim,
                                      self.state if bound else None, ctx.state_slots if bound else None, **kw)
 
@@ -106,8 +122,9 @@ class GatedNorm(nn.Module):
         else:
             self.register_parameter("weight", None)
 
-    def forward(self, y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
-        return ops.gated_norm(y, gate, self.weight, self.eps, self.groups, self.gate_first, self.gate_act)
+    def forward(self, y: torch.Tensor, gate: torch.Tensor | None, dtype=None) -> torch.Tensor:
+        """gate None: the grouped norm alone, written in ``dtype``."""
+        return ops.gated_norm(y, gate, self.weight, self.eps, self.groups, self.gate_first, self.gate_act, dtype=dtype)
 
 
 class VarSizeAttention(nn.Module):
@@ -153,6 +170,61 @@ class VarSizeAttention(nn.Module):
             return ops.attn_generic(q, self.k_cache, self.v_cache, spans, self.scale, self.num_kv_heads, self.vdim,
                                     block_tables=ctx.block_tables, window=self.window)
         return ops.attn_generic(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, window=self.window)
+
+
+class MixedHeadAttention(nn.Module):
+    """Causal softmax attention whose heads are mixed BEFORE the softmax (``talk`` [H, H], s'_h = sum_g talk[h, g] s_g),
+    with an optional linear distance bias per head (s_h(i, j) = scale q.k - slope_h (i - j); ``slope_base`` b gives
+    slope_h = 2^(-b (h + 1) / H)), an optional learned ``sink`` per head that joins the softmax denominator without a
+    key or value, and an optional sliding window. Keys/values live in paged caches ``k_cache`` [nb, bs, G*dim] /
+    ``v_cache`` [nb, bs, G*vdim] written by the caller's fused epilogue -- or, with ``kv_source`` (another
+    MixedHeadAttention of the same head counts), in THAT layer's caches: this layer then projects queries only and
+    reads the other layer's keys (as cached, after their norm) and values through the same block tables."""
+
+    def __init__(self, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0,
+                 slope_base: float | None = None, talk: bool = True, sink: bool = True, kv_source=None):
+        super().__init__()
+        self.num_heads, self.num_kv_heads, self.dim, self.vdim = num_heads, num_kv_heads, dim, vdim
+        self.scale, self.window = float(scale), int(window)
+        if slope_base is not None:
+            slopes = [2.0 ** (-float(slope_base) * (h + 1) / num_heads) for h in range(num_heads)]
+            self.register_buffer("slopes", torch.tensor(slopes, dtype=F32), persistent=False)
+        else:
+            self.slopes = None
+        if talk:
+            self.talk = nn.Parameter(torch.eye(num_heads, dtype=F32))
+        else:
+            self.register_parameter("talk", None)
+        if sink:
+            self.sink = small_param(num_heads)
+        else:
+            self.register_parameter("sink", None)
+        if kv_source is not None and (kv_source.num_kv_heads, kv_source.dim, kv_source.vdim) != (num_kv_heads, dim, vdim):
+            raise ValueError("a layer that borrows keys and values needs the lender's kv head count and sizes")
+        object.__setattr__(self, "kv_source", kv_source)          # not a submodule: the lender owns its parameters
+        self.k_cache = torch.tensor([])
+        self.v_cache = torch.tensor([])
+        self.layer_id = -1
+        self.step_kv = None                         # this step's (k, v) rows, kept for a borrower when no cache is bound
+
+    def cache_rows(self) -> tuple[int, int]:
+        if self.kv_source is not None:
+            return 0, 0                             # the runner binds the lender's caches
+        return self.num_kv_heads * self.dim, self.num_kv_heads * self.vdim
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor | None = None, v: torch.Tensor | None = None) -> torch.Tensor:
+        """q [T, H, dim]; k [T, G, dim], v [T, G, vdim]: this step's rows (None for a borrower)."""
+        ctx = get_context()
+        if self.kv_source is None:
+            self.step_kv = (k, v)
+        else:
+            k, v = self.kv_source.step_kv
+        spans = ops.StepSpans.of(ctx)
+        kw = dict(window=self.window, slopes=self.slopes, talk=self.talk, sink=self.sink)
+        if self.k_cache.numel() > 0 and ctx.block_tables is not None:
+            return ops.mixed_attn(q, self.k_cache, self.v_cache, spans, self.scale, self.num_kv_heads, self.vdim,
+                                  block_tables=ctx.block_tables, **kw)
+        return ops.mixed_attn(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, **kw)
 
 
 class DeltaRule(nn.Module):

@@ -4,7 +4,8 @@ The dense families of the hot-path scope and the Qwen3-MoE stack (SURVEY.md 8 f4
 the reference's registry (models/models_map.py) also lists its MiniCPM and vision-language stacks,
 which this build deliberately leaves out. Zegopel (a hybrid of softmax attention, lightning attention and
 Mamba-2 layers) and Nirelix (retention, gated delta rule and latent attention on a residual kept in several
-streams) are additions; their config.json names them with an ``"architecture"`` string (config.NativeConfig). Qwen2 checkpoints are served by the Qwen3 class, as in the reference:
+streams) and Fitevik (HGRN2 recurrences and attention with mixed heads, a distance bias and a sink, on a residual
+with the norm on each sublayer's output) are additions; their config.json names them with an ``"architecture"`` string (config.NativeConfig). Qwen2 checkpoints are served by the Qwen3 class, as in the reference:
 the config's ``attention_bias`` decides between QKV bias (Qwen2) and QK-norm (Qwen3).
 """
 from __future__ import annotations
@@ -12,6 +13,7 @@ from __future__ import annotations
 from .llama import LlamaForCausalLM
 from .qwen3 import Qwen3ForCausalLM
 from .qwen3_moe import Qwen3MoeForCausalLM
+from .fitevik import FitevikForCausalLM
 from .nirelix import NirelixForCausalLM
 from .zegopel import ZegopelForCausalLM
 
@@ -27,5 +29,6 @@ for _arch, _cls in (("Qwen3ForCausalLM", Qwen3ForCausalLM),
                     ("Qwen3MoeForCausalLM", Qwen3MoeForCausalLM),
                     ("LlamaForCausalLM", LlamaForCausalLM),
                     ("Zegopel", ZegopelForCausalLM),
-                    ("Nirelix", NirelixForCausalLM)):
+                    ("Nirelix", NirelixForCausalLM),
+                    ("Fitevik", FitevikForCausalLM)):
     register(_arch, _cls)

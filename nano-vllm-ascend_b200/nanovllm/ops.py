@@ -695,22 +695,30 @@ def unitnorm_temp_cache(qkv, positions, eps, temp_coef, temp_every, num_heads, n
     return qkv
 
 
-def gated_norm(y, gate, weight, eps, groups=1, gate_first=False, gate_act="sigmoid"):
+def gated_norm(y, gate, weight, eps, groups=1, gate_first=False, gate_act="sigmoid", dtype=None):
     """y [rows, n] (fp32 or gate's dtype), gate [rows, n] (row-strided view allowed) -> [rows, n] in gate's dtype.
     weight fp32 [n]: RMS norm over each of `groups` equal parts, before (gate_first=False) or after the gate;
-    weight None: the gate alone."""
+    weight None: the gate alone. gate None (with a weight): the grouped norm alone, output in `dtype`."""
     _need_cuda(y, gate, weight)
     _f32(weight)
     rows, n = y.shape
-    if not y.is_contiguous() or gate.shape != y.shape or gate.stride(1) != 1:
-        raise ValueError("y contiguous [rows, n]; gate [rows, n] with unit inner stride")
-    if y.dtype not in (torch.float32, gate.dtype):
+    if gate is None:
+        if weight is None or dtype is None:
+            raise ValueError("without a gate: give the norm weight and the output dtype")
+        gate_act = "none"
+    elif gate.shape != y.shape or gate.stride(1) != 1:
+        raise ValueError("gate [rows, n] with unit inner stride")
+    else:
+        dtype = gate.dtype
+    if not y.is_contiguous():
+        raise ValueError("y contiguous [rows, n]")
+    if y.dtype not in (torch.float32, dtype):
         raise TypeError("y must be fp32 or of the gate's dtype")
-    out = torch.empty(rows, n, dtype=gate.dtype, device=gate.device)
+    out = torch.empty(rows, n, dtype=dtype, device=y.device)
     _C.check(_C.load().b200_gated_norm(out.data_ptr(), y.data_ptr(), 1 if y.dtype == torch.float32 else 0,
-                                       gate.data_ptr(), gate.stride(0) if rows > 1 else n, _ptr(weight), float(eps),
-                                       rows, n, int(groups), 1 if gate_first else 0,
-                                       {"sigmoid": 0, "silu": 1}[gate_act], _dt3(gate), _stream()),
+                                       _ptr(gate), (gate.stride(0) if rows > 1 else n) if gate is not None else n,
+                                       _ptr(weight), float(eps), rows, n, int(groups), 1 if gate_first else 0,
+                                       {"sigmoid": 0, "silu": 1, "none": 2}[gate_act], _DT3[dtype], _stream()),
              "b200_gated_norm")
     return out
 
@@ -727,6 +735,123 @@ def act_and_mul(x, act="silu"):
     out = torch.empty(rows, inter, dtype=x.dtype, device=x.device)
     _C.check(_C.load().b200_act_and_mul(out.data_ptr(), x.data_ptr(), rows, inter, _ACTS[act], _dt3(x), _stream()),
              "b200_act_and_mul")
+    return out
+
+
+_PLAIN_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu2": 3}
+
+
+def act_only(x, act="relu2"):
+    """act(x) elementwise for a feed-forward without a gate: silu | relu | gelu_tanh | relu2 (the square of relu)."""
+    _need_cuda(x)
+    if not x.is_contiguous():
+        raise ValueError("act_only input must be contiguous")
+    out = torch.empty_like(x)
+    _C.check(_C.load().b200_act_only(out.data_ptr(), x.data_ptr(), x.numel(), _PLAIN_ACTS[act], _dt3(x), _stream()),
+             "b200_act_only")
+    return out
+
+
+def norm_residual_(residual, y, w, b, eps, dtype, kind="layer", offset=0.0, accumulate=True, y_index=None, y2=None,
+                   y2_index=None, want_h=True):
+    """A norm on a sublayer's OUTPUT, then the residual: residual (fp32 [rows, hidden], in place) <- (residual if
+    accumulate else 0) + norm(y [+ y2]); returns the new residual in `dtype` (the next sublayer reads the stream
+    itself). kind "layer": (u - mean) / sqrt(var + eps) * w + b; "rms": u / sqrt(mean u^2 + eps) * (offset + w).
+    y_index / y2_index (int64 [rows]): rows of y / y2 are gathered by index (clamped to the table) -- token embedding
+    plus learned position plus norm in one launch."""
+    _need_cuda(residual, y, w, b, y_index, y2, y2_index)
+    _f32(residual, w, b)
+    rows, hidden = residual.shape
+    for t, idx in ((y, y_index), (y2, y2_index)):
+        if t is None:
+            continue
+        if not t.is_contiguous() or t.shape[-1] != hidden or t.dtype != dtype or (idx is None and t.shape[0] != rows):
+            raise ValueError("y / y2: contiguous [rows or table, hidden] of the model dtype")
+        if idx is not None and (idx.dtype != torch.int64 or not idx.is_contiguous() or idx.numel() != rows):
+            raise TypeError("row indices are contiguous int64 [rows]")
+    h = torch.empty(rows, hidden, dtype=dtype, device=residual.device) if want_h else None
+    _C.check(_C.load().b200_norm_residual(_ptr(h), residual.data_ptr(), y.data_ptr(), _ptr(y_index), y.shape[0],
+                                          _ptr(y2), _ptr(y2_index), y2.shape[0] if y2 is not None else 0,
+                                          w.data_ptr(), _ptr(b), float(eps), float(offset),
+                                          {"layer": 0, "rms": 1}[kind], 1 if accumulate else 0, rows, hidden,
+                                          _DT3[dtype], _stream()), "b200_norm_residual")
+    return h
+
+
+def rownorm_cache(x, nq, nk, nv, wq, wk, eps, k_cache=None, v_cache=None, slots=None):
+    """In place on x [T, nq + nk + nv] (unit inner stride): the nq query columns and the nk key columns are each
+    divided by the root mean square of ALL their columns (every head at once) and multiplied by the plain weights wq,
+    wk; k and v rows are stored at `slots` of the paged caches [nb, bs, nk] / [nb, bs, nv] when given. nk = nv = 0: a
+    layer that projects queries only."""
+    _need_cuda(x, wq, wk, k_cache, v_cache, slots)
+    _f32(wq, wk)
+    T = x.shape[0]
+    if x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != nq + nk + nv or wq.numel() != nq or (nk and wk.numel() != nk):
+        raise ValueError("x must be [T, nq + nk + nv] with unit inner stride; one weight per q / k column")
+    have = k_cache is not None and k_cache.numel() > 0 and nk > 0
+    bs = 0
+    if have:
+        _, bs = _cache_dims(k_cache, nk)
+        _cache_dims(v_cache, nv)
+        if slots.dtype != torch.int32 or not slots.is_contiguous():
+            raise TypeError("slots must be contiguous int32")
+        if k_cache.dtype != x.dtype or v_cache.dtype != x.dtype:
+            raise TypeError("caches must have the activations' dtype")
+    _C.check(_C.load().b200_rownorm_cache(x.data_ptr(), x.stride(0) if T > 1 else x.shape[1], wq.data_ptr(), _ptr(wk),
+                                          float(eps), k_cache.data_ptr() if have else None,
+                                          v_cache.data_ptr() if have else None, slots.data_ptr() if have else None,
+                                          1 if (have and slots.dim() == 2) else 0, bs, T, nq, nk, nv, _dt3(x),
+                                          _stream()), "b200_rownorm_cache")
+    return x
+
+
+def gate_prep(q, f, bias, lower):
+    """q, f [T, n] (row-strided views) -> (silu(q), lower + (1 - lower) * sigmoid(f + bias)), both fp32 [T, n]: the
+    query and the lower-bounded forget gate of a gated linear recurrence; bias, lower fp32 [n] or None (0)."""
+    _need_cuda(q, f, bias, lower)
+    _f32(bias, lower)
+    T, n = q.shape
+    if f.shape != q.shape or q.stride(1) != 1 or f.stride(1) != 1 or q.dtype != f.dtype:
+        raise ValueError("q, f [T, n] with unit inner stride, one dtype")
+    q32 = torch.empty(T, n, dtype=torch.float32, device=q.device)
+    f32 = torch.empty(T, n, dtype=torch.float32, device=q.device)
+    stride = lambda t: t.stride(0) if T > 1 else n
+    _C.check(_C.load().b200_gate_prep(q32.data_ptr(), f32.data_ptr(), q.data_ptr(), stride(q), f.data_ptr(), stride(f),
+                                      _ptr(bias), _ptr(lower), T, n, _dt3(q), _stream()), "b200_gate_prep")
+    return q32, f32
+
+
+def mixed_attn(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tables=None, window=0, slopes=None,
+               talk=None, sink=None):
+    """Causal softmax attention whose heads are mixed BEFORE the softmax. Shapes, paging, spans and the window as in
+    attn_generic. slopes fp32 [H]: s_h(i, j) = scale q.k - slopes[h] (i - j); talk fp32 [H, H]: s'_h = sum_g
+    talk[h, g] s_g; sink fp32 [H]: exp(sink[h]) joins the softmax denominator (no key, no value). Each may be None."""
+    _need_cuda(q, k, v, block_tables, slopes, talk, sink)
+    _f32(slopes, talk, sink)
+    T, H, dim = q.shape
+    if q.stride(2) != 1 or q.stride(1) != dim:
+        raise ValueError("q must be contiguous in (heads, dim)")
+    G = num_kv_heads
+    if (talk is not None and talk.shape != (H, H)) or any(t is not None and t.numel() != H for t in (slopes, sink)):
+        raise ValueError("talk [H, H]; slopes, sink [H]")
+    if block_tables is not None:
+        if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+            raise TypeError("block_tables must be row-major int32")
+        _, bs = _cache_dims(k, G * dim)
+        _cache_dims(v, G * vdim)
+        ks, vs, bt_ptr, bt_stride = G * dim, G * vdim, block_tables.data_ptr(), block_tables.stride(0)
+    else:
+        if k.stride(2) != 1 or k.stride(1) != dim or v.stride(2) != 1 or v.stride(1) != vdim:
+            raise ValueError("k/v must be contiguous in (heads, dim)")
+        bs, bt_ptr, bt_stride = 0, None, 0
+        ks = k.stride(0) if k.shape[0] > 1 else G * dim
+        vs = v.stride(0) if v.shape[0] > 1 else G * vdim
+    out = torch.empty(T, H * vdim, dtype=q.dtype, device=q.device)
+    cu_q, cu_k, ctx = spans.ptrs()
+    _C.check(_C.load().b200_mixed_attn(out.data_ptr(), q.data_ptr(), q.stride(0) if T > 1 else H * dim, k.data_ptr(),
+                                       ks, v.data_ptr(), vs, bt_ptr, bt_stride, bs, cu_q, cu_k, ctx, spans.num_seqs,
+                                       spans.max_q, H, G, dim, vdim, float(scale), int(window), _ptr(slopes),
+                                       _ptr(talk), _ptr(sink), _dt3(q), _stream()), "b200_mixed_attn")
     return out
 
 
@@ -765,13 +890,15 @@ def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tab
 
 
 def linear_recurrence(q, k, v, spans: StepSpans, num_heads, groups, kdim, vdim, state=None, state_slots=None,
-                      decay=None, act_silu=False, dt=None, dt_bias=None, a_log=None, d_skip=None):
+                      decay=None, act_silu=False, dt=None, dt_bias=None, a_log=None, d_skip=None, tied_gate=False):
     """Per head S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t, S fp32 [kdim, vdim] carried in
     state[slot] ([slots, H, kdim, vdim] fp32) between steps. q, k [T, groups*kdim] (head h reads group
     h // (H / groups)), v [T, H*vdim]; row-strided views allowed. Returns fp32 [T, H*vdim].
       decay given (fp32 [H]): a_t = decay_h, b_t = 1; act_silu applies silu to q, k, v as they are read.
       dt given ([T, H]):      step = softplus(dt + dt_bias_h), a_t = exp(-exp(a_log_h) * step), b_t = step, and
-                              o_t += d_skip_h * v_t."""
+                              o_t += d_skip_h * v_t.
+      tied_gate:              k holds a forget gate f per key channel (fp32, like q) that also decides what is written:
+                              S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T."""
     _need_cuda(q, k, v, state, state_slots, decay, dt, dt_bias, a_log, d_skip)
     _f32(decay, dt_bias, a_log, d_skip, state)
     T = q.shape[0]
@@ -779,13 +906,15 @@ def linear_recurrence(q, k, v, spans: StepSpans, num_heads, groups, kdim, vdim, 
     for t, n in ((q, groups * kdim), (k, groups * kdim), (v, num_heads * vdim)):
         if t.dim() != 2 or t.shape[1] != n or t.stride(1) != 1 or (t.dtype != q.dtype and not (qk_f32 and t is v)):
             raise ValueError("q, k [T, groups*kdim] and v [T, H*vdim] with unit inner stride, one dtype")
-    if qk_f32 and (decay is None or act_silu):
-        raise ValueError("fp32 q/k beside 16-bit v: constant-decay form without activation only")
+    if tied_gate and (q.dtype != torch.float32 or decay is not None or dt is not None or act_silu):
+        raise ValueError("tied-gate form: fp32 q and gate, no decay, dt or activation")
+    if qk_f32 and not tied_gate and (decay is None or act_silu):
+        raise ValueError("fp32 q/k beside 16-bit v: constant-decay or tied-gate form without activation only")
     if state is not None and tuple(state.shape[1:]) != (num_heads, kdim, vdim):
         raise ValueError(f"state must be [slots, {num_heads}, {kdim}, {vdim}]")
     if state is not None and (state_slots is None or state_slots.dtype != torch.int32):
         raise TypeError("state_slots must be int32")
-    mode = 0 if decay is not None else 1
+    mode = 2 if tied_gate else 0 if decay is not None else 1
     if mode == 1 and (dt is None or dt.shape != (T, num_heads) or dt.stride(1) != 1 or dt.dtype != q.dtype):
         raise ValueError("dt must be [T, H] of q's dtype")
     out = torch.empty(T, num_heads * vdim, dtype=torch.float32, device=q.device)
@@ -981,15 +1110,32 @@ def moe_route_grouped(router_logits, bias, top_k, groups=1, keep=1, scale=1.0):
     return ids, w
 
 
-def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan) -> torch.Tensor:
-    """Expert MLPs down(silu(gate x) * up x) and the weighted combine for any sizes and dtypes (fp32 included):
-    x [T, hidden]; w13 [E, 2*inter, hidden]; w2 [E, hidden, inter]; topk_weights fp32 [T, k]."""
+def moe_route_topk(router_logits, bias, top_k):
+    """The top_k largest of router_logits + bias (fp32 [T, E]; bias fp32 [E] or None), weighted by the softmax over
+    the chosen logits only -> (topk_ids int32 [T, k], topk_weights fp32 [T, k]). Ties go to the lower index."""
+    _need_cuda(router_logits, bias)
+    _f32(bias)
+    if router_logits.dtype != torch.float32 or router_logits.stride(1) != 1:
+        raise TypeError("router logits are fp32 with unit inner stride")
+    T, E = router_logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=router_logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=router_logits.device)
+    _C.check(_C.load().b200_moe_route_topk(ids.data_ptr(), w.data_ptr(), router_logits.data_ptr(),
+                                           router_logits.stride(0) if T > 1 else E, _ptr(bias), T, E, int(top_k),
+                                           _stream()), "b200_moe_route_topk")
+    return ids, w
+
+
+def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan, act=None) -> torch.Tensor:
+    """Expert MLPs and the weighted combine for any sizes and dtypes (fp32 included): x [T, hidden]; w2 [E, hidden,
+    inter]; topk_weights fp32 [T, k]. act None: gated experts down(silu(gate x) * up x) with w13 [E, 2*inter, hidden];
+    act "silu" | "relu" | "gelu_tanh" | "relu2": experts without a gate, down(act(up x)) with w13 [E, inter, hidden]."""
     _need_cuda(x, w13, w2, topk_weights)
     _f32(topk_weights)
     T, hidden = x.shape
     E, two_i, _ = w13.shape
-    inter, k = two_i // 2, plan.top_k
-    if w13.shape != (E, 2 * inter, hidden) or w2.shape != (E, hidden, inter) or E != plan.num_local:
+    inter, k = (two_i // 2 if act is None else two_i), plan.top_k
+    if w13.shape != (E, two_i, hidden) or w2.shape != (E, hidden, inter) or E != plan.num_local:
         raise ValueError("expert weight shapes do not match")
     if not (w13.is_contiguous() and w2.is_contiguous()) or x.stride(1) != 1 or x.dtype != w13.dtype or x.dtype != w2.dtype:
         raise ValueError("contiguous expert weights of x's dtype; x row-major")
@@ -1000,7 +1146,8 @@ def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan) -> torch.Tensor
     out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
     _C.check(lib.b200_moe_gemm_generic(h.data_ptr(), x.data_ptr(), x.stride(0) if T > 1 else hidden, w13.data_ptr(),
                                        plan.offsets.data_ptr(), plan.sorted_pair.data_ptr(), pairs, hidden, inter, E,
-                                       k, 1, _dt3(x), _stream()), "b200_moe_gemm_generic (gate_up)")
+                                       k, 1 if act is None else 2 + _PLAIN_ACTS[act], _dt3(x), _stream()),
+             "b200_moe_gemm_generic (up)")
     _C.check(lib.b200_moe_gemm_generic(y.data_ptr(), h.data_ptr(), inter, w2.data_ptr(), plan.offsets.data_ptr(),
                                        plan.sorted_pair.data_ptr(), pairs, inter, hidden, E, k, 0, _dt3(x),
                                        _stream()), "b200_moe_gemm_generic (down)")
