@@ -24,7 +24,8 @@ the all-reduce form and its latency, and the same workload at TP=1 (rank 0) for 
 `--impl reference` times only the CPU reference arm.
 `--hybrid` leaves the contract workload aside: the Zegopel hybrid decoder beside the dense decoder of the same width
 (prefill and decode throughput through the engine) and the rooflines of its kernels beside their like kernels;
-`--hybrid --design nirelix` does the same for the Nirelix decoder beside the Zegopel decoder of the same width.
+`--hybrid --design nirelix` does the same for the Nirelix decoder beside the Zegopel decoder of the same width, and
+`--hybrid --design fitevik` for the Fitevik decoder beside the Nirelix decoder of the same width.
 """
 from __future__ import annotations
 
@@ -110,8 +111,9 @@ def parse_args():
                          "decoder beside the dense decoder of the same width and depth, and its kernels' rooflines")
     ap.add_argument("--hybrid-pairs", default=None,
                     help="model:model,... (default zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b; with --design "
-                         "nirelix: nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k)")
-    ap.add_argument("--design", default="zegopel", choices=["zegopel", "nirelix"],
+                         "nirelix: nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k; with --design fitevik: "
+                         "fitevik-1k:nirelix-1k,fitevik-2k:nirelix-2k)")
+    ap.add_argument("--design", default="zegopel", choices=["zegopel", "nirelix", "fitevik"],
                     help="with --hybrid: whose presets and kernel table are measured")
     ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8"],
                     help="fp8: e4m3 KV cache (an extra line; the contract line is the default bf16 cache)")
@@ -867,6 +869,167 @@ def nirelix_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
     return rows
 
 
+def fitevik_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
+    """The kernels that the Fitevik decoder adds, alone, at the layer sizes of a `width`-wide model, as a prompt step
+    (`seqs` x tokens/seqs) and as a decode step (`seqs` rows at that context), each beside the like kernel of the
+    Nirelix (or Zegopel) decoder. frac = algorithmic bytes / time / measured copy bandwidth."""
+    from nanovllm import ops
+    dev, bf = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=g)
+    H = width // head_dim
+    G = max(1, H // 4)
+    rows = []
+
+    def add(name, step, fn, nbytes, like=None, like_fn=None, like_bytes=None, flops=None, like_flops=None):
+        t = _timed(fn, flush)
+        row = {"kernel": name, "step": step, "us": round(t * 1e6, 1), "GB/s": round(nbytes / t / 1e9),
+               "frac_of_measured_copy": round(nbytes / t / 1e9 / peak_gbs, 3)}
+        if flops:
+            row["TFLOP/s"] = round(flops / t / 1e12, 2)
+        if like_fn is not None:
+            tl = _timed(like_fn, flush)
+            row["like"] = {"kernel": like, "us": round(tl * 1e6, 1),
+                           "frac_of_measured_copy": round(like_bytes / tl / 1e9 / peak_gbs, 3)}
+            if like_flops:
+                row["like"]["TFLOP/s"] = round(like_flops / tl / 1e12, 2)
+            row["times_as_far_from_roofline_as_like"] = round((like_bytes / tl) / (nbytes / t), 2)
+            if flops and like_flops:
+                row["times_as_far_from_flop_roofline_as_like"] = round((like_flops / tl) / (flops / t), 2)
+        rows.append(row)
+
+    for step, T in (("prompt", tokens), ("decode", seqs)):
+        per = T // seqs if step == "prompt" else 1
+        ctx = tokens // seqs
+        if step == "prompt":
+            cu = torch.arange(0, T + 1, per, dtype=torch.int32, device=dev)
+            spans = ops.StepSpans(cu, cu, None, per)
+        else:
+            spans = ops.StepSpans(None, None, torch.full((T,), ctx, dtype=torch.int32, device=dev))
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        pos = (torch.arange(T, device=dev) % max(per, 1) + (0 if step == "prompt" else ctx - 1)).contiguous()
+        # residual path: layer norm on the sublayer's output + add, beside the add + two RMS norms / the 1-stream form
+        y, res, res2 = rnd(T, width).to(bf), rnd(T, width), rnd(T, width)
+        w1, w2 = rnd(width), rnd(width)
+        add("norm_residual(layer norm on the output)", step, lambda: ops.norm_residual_(res, y, w1, w2, 1e-5, bf),
+            T * width * 12, "residual_add_norms", lambda: ops.residual_add_norms_(y, res2, w1, w2, 1e-6), T * width * 12)
+        emb, ptab = rnd(32768, width).to(bf), rnd(8192, width).to(bf)
+        ids = torch.randint(0, 32768, (T,), device=dev, generator=g)
+        add("norm_residual(embedding + position, gathered)", step,
+            lambda: ops.norm_residual_(res, emb, w1, w2, 1e-5, bf, accumulate=False, y_index=ids, y2=ptab, y2_index=pos),
+            T * width * 10)
+        ff = 3 * width
+        up = rnd(T, 2 * ff).to(bf)
+        up1 = up[:, :ff].contiguous()
+        add("act_only(relu squared)", step, lambda: ops.act_only(up1, "relu2"), T * ff * 4,
+            "act_and_mul(relu)", lambda: ops.act_and_mul(up, "relu"), T * ff * 6)
+        # attention preparation: norms over the whole q and k projections + cache write
+        nq, nk = H * head_dim, G * head_dim
+        qkv = rnd(T, nq + 2 * nk).to(bf)
+        qkv2 = qkv.clone()
+        nb = (T + 15) // 16 + 1
+        kc = torch.zeros(nb, 16, nk, dtype=bf, device=dev)
+        vc = torch.zeros(nb, 16, nk, dtype=bf, device=dev)
+        sl = torch.arange(T, dtype=torch.int32, device=dev)
+        wq, wk = rnd(nq), rnd(nk)
+        prep_bytes = T * (2 * (nq + nk) * 2 + 3 * nk * 2)
+        add("rownorm_cache", step, lambda: ops.rownorm_cache(qkv, nq, nk, nk, wq, wk, 1e-5, kc, vc, sl), prep_bytes,
+            "unitnorm_temp_cache", lambda: ops.unitnorm_temp_cache(qkv2, pos, 1e-6, 0.1, 1024, H, G, head_dim, head_dim,
+                                                                   kc, vc, sl), prep_bytes)
+        # the recurrence: gate and query in fp32, then the tied-gate form (like: delta_prep and the delta rule)
+        p3 = rnd(T, 3 * nq).to(bf)
+        gb, lower = rnd(nq), torch.rand(nq, device=dev, generator=g) * 0.9
+        Gd = max(1, H // 2)
+        ngk = Gd * head_dim
+        qkc = rnd(T, 2 * ngk + nq).to(bf)
+        a_in, b_in = rnd(T, nq).to(bf), rnd(T, H).to(bf)
+        dtb, alog = rnd(nq), -torch.rand(H, device=dev, generator=g) * 2 - 1
+        add("gate_prep", step, lambda: ops.gate_prep(p3[:, :nq], p3[:, nq:2 * nq], gb, lower), T * nq * (4 + 8),
+            "delta_prep", lambda: ops.delta_prep(qkc[:, :2 * ngk], a_in, b_in, dtb, alog, H, Gd, head_dim, 1e-6,
+                                                 head_dim ** -0.5), T * (2 * ngk * 6 + nq * 6 + H * 6))
+        q32, f32 = ops.gate_prep(p3[:, :nq], p3[:, nq:2 * nq], gb, lower)
+        dq32, dec, beta = ops.delta_prep(qkc[:, :2 * ngk], a_in, b_in, dtb, alog, H, Gd, head_dim, 1e-6, head_dim ** -0.5)
+        st = torch.zeros(seqs + 1, H, head_dim, head_dim, device=dev)
+        state_bytes = 2 * seqs * H * head_dim * head_dim * 4 if step == "decode" else 0
+        add("linear_recurrence(tied forget gate per channel)", step,
+            lambda: ops.linear_recurrence(q32, f32, p3[:, 2 * nq:], spans, H, H, head_dim, head_dim, st, slots,
+                                          tied_gate=True), T * nq * (4 + 4 + 2 + 4) + state_bytes,
+            "delta_rule", lambda: ops.delta_rule(dq32[:, :ngk], dq32[:, ngk:], qkc[:, 2 * ngk:], dec, beta, spans, H, Gd,
+                                                 head_dim, head_dim, st, slots),
+            T * (2 * ngk * 4 + nq * 4 + nq * 2 + nq * 4) + state_bytes,
+            flops=4.0 * T * H * head_dim * head_dim, like_flops=8.0 * T * H * head_dim * head_dim)
+        o32, gate = rnd(T, nq), rnd(T, nq).to(bf)
+        ones = torch.ones(nq, device=dev)
+        add("gated_norm(a norm per head, no gate)", step,
+            lambda: ops.gated_norm(o32, None, ones, 1e-5, groups=H, dtype=bf), T * nq * 6,
+            "gated_norm(a norm per head, silu gate)", lambda: ops.gated_norm(o32, gate, ones, 1e-6, groups=H, gate_act="silu"),
+            T * nq * 8)
+        # attention: heads mixed before the softmax, distance bias, sink, window 512 over paged keys and values
+        window = 512
+        nbl = seqs * (-(-ctx // 16)) + 1
+        kcache = (torch.randn(nbl, 16, nk, device=dev, generator=g) * 0.3).to(bf)
+        vcache = (torch.randn(nbl, 16, nk, device=dev, generator=g) * 0.3).to(bf)
+        tables = torch.arange(seqs * (-(-ctx // 16)), dtype=torch.int32, device=dev).view(seqs, -1)
+        qh = (rnd(T, H, head_dim) * 0.3).to(bf)
+        talk = torch.eye(H, device=dev) + 0.1 * rnd(H, H)
+        sink = rnd(H)
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+        keys = min(window, ctx)
+        band = sum(min(window, i + 1) for i in range(per)) * seqs if step == "prompt" else T * keys
+        R, dr = 4 * head_dim, head_dim // 2
+        lcache = (torch.randn(nbl, 16, R + dr, device=dev, generator=g) * 0.3).to(bf)
+        qx = (rnd(T, H, R + dr) * 0.3).to(bf)
+        from nanovllm.layers.seq_mixers import LatentAttention, MixedHeadAttention
+        from nanovllm.utils.context import get_context, reset_context, set_context
+        la = LatentAttention(H, head_dim, dr, head_dim, R, 0.07, window=window)
+        la.k_cache = lcache
+        mh = MixedHeadAttention(H, G, head_dim, head_dim, 0.3, window=window, slope_base=8.0).to(dev)
+        mh.talk.data.copy_(talk)
+        mh.sink.data.copy_(sink)
+        mh.k_cache, mh.v_cache = kcache, vcache
+        if step == "prompt":
+            set_context(True, cu_seqlens_q=spans.cu_q, cu_seqlens_k=spans.cu_k, max_seqlen_q=per, max_seqlen_k=per,
+                        block_tables=tables, block_size=16, host_spans=[(i * per, per, per) for i in range(seqs)])
+            like_fn = lambda: la._prefill_by_products(qx, None, get_context(), True)
+        else:
+            set_context(False, context_lens=spans.ctx_lens, block_tables=tables, block_size=16)
+            like_fn = lambda: la._decode_window_by_products(qx, get_context())
+        att_bytes = T * 2 * nq * 2 + seqs * min(ctx, keys + per) * 2 * nk * 2
+        lat_bytes = T * H * (R + dr + R) * 2 + seqs * min(ctx, keys + per) * (R + dr) * 2
+        add("mixed-head attention as the model runs it (window 512)", step, lambda: mh(qh), att_bytes,
+            "latent attention by products (window 512)", like_fn, lat_bytes,
+            flops=4.0 * band * H * head_dim, like_flops=2.0 * band * H * (2 * R + dr))
+        add("mixed_attn kernel alone (window 512)", step,
+            lambda: ops.mixed_attn(qh, kcache, vcache, spans, 0.3, G, head_dim, block_tables=tables, window=window,
+                                   slopes=slopes, talk=talk, sink=sink), att_bytes,
+            "attn_generic(latent rows, window 512)",
+            lambda: ops.attn_generic(qx, lcache, None, spans, 0.07, 1, R, block_tables=tables, window=window), lat_bytes,
+            flops=4.0 * band * H * head_dim, like_flops=2.0 * band * H * (2 * R + dr))
+        reset_context()
+        # mixture of experts: router, then experts without a gate (like: the grouped sigmoid router, gated experts)
+        E, top, ffe = 16, 2, width // 2
+        x = rnd(T, width).to(bf)
+        logits = rnd(T, E)
+        corr = rnd(E) * 0.1
+        add("moe_route_topk", step, lambda: ops.moe_route_topk(logits, corr, top), T * (E * 4 + top * 8),
+            "moe_route_grouped", lambda: ops.moe_route_grouped(logits, corr, top, 4, 2, 1.5), T * (E * 4 + top * 8))
+        from nanovllm.layers.moe import GroupedSigmoidMoe, TopkSoftmaxMoe
+        with torch.device(dev):
+            ours, theirs = TopkSoftmaxMoe(width, ffe, E, top).to(bf), GroupedSigmoidMoe(width, ffe, E, top, 4, 2, 1.5).to(bf)
+        for m_ in (ours, theirs):
+            for p_ in m_.parameters():
+                p_.data.copy_((torch.randn(p_.shape, device=dev, generator=g) * 0.03).to(p_.dtype))
+            m_.router.data = m_.router.data.float()
+        ours.router_bias.data, theirs.correction.data = ours.router_bias.data.float(), theirs.correction.data.float()
+        with torch.inference_mode():
+            add("mixture of experts without a gate (router + experts)", step, lambda: ours(x),
+                2 * E * ffe * width * 2 + T * width * 4,
+                "mixture of gated experts (router + experts)", lambda: theirs(x), 3 * E * ffe * width * 2 + T * width * 4,
+                flops=4.0 * T * top * ffe * width, like_flops=6.0 * T * top * ffe * width)
+    return rows
+
+
 def hybrid_compare(args):
     """--hybrid: the Zegopel presets beside the dense presets of the same width and depth, each through the engine
     (LLM.add_request / LLM.step; prompt steps, then CUDA-graph decode steps), plus the kernel table."""
@@ -880,8 +1043,9 @@ def hybrid_compare(args):
            "dtype": "bf16", "data": "synthetic (random-init weights, random token ids)",
            "config": {"batch": B, "ctx": ctx, "block_size": args.block_size, "l2": "prompts and caches exceed L2; "
                       "kernel table: 256 MB flush before every timed launch"}, "models": [], "peak_source": peak_src}
-    pairs = args.hybrid_pairs or ("nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k" if args.design == "nirelix" else
-                                  "zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b")
+    pairs = args.hybrid_pairs or {"nirelix": "nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k",
+                                  "fitevik": "fitevik-1k:nirelix-1k,fitevik-2k:nirelix-2k"}.get(
+        args.design, "zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b")
     out["design"] = args.design
     for pair in pairs.split(","):
         for name in pair.split(":"):
@@ -902,7 +1066,7 @@ def hybrid_compare(args):
             release(llm)
             del llm
             torch.cuda.empty_cache()
-    table = nirelix_kernel_table if args.design == "nirelix" else hybrid_kernel_table
+    table = {"nirelix": nirelix_kernel_table, "fitevik": fitevik_kernel_table}.get(args.design, hybrid_kernel_table)
     out["kernels"] = {"width_1024_head_128": table(1024, 128, 16384, 16, peak),
                       "width_2048_head_64": table(2048, 64, 16384, 16, peak)}
     out["clocks"] = clocks.stop()
