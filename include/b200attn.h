@@ -299,6 +299,11 @@ int b200_moe_gemm_gate_up(void* h, const void* x, const void* w13, const int32_t
                           const int32_t* sorted_pair, int32_t hidden, int32_t inter,
                           int32_t num_local, int32_t top_k, int64_t x_stride, int32_t dtype,
                           b200_stream_t stream);
+/* Experts without a gate: h[pos, :inter] = act(x[sorted_pair[pos] / top_k] . w1[e]^T in dtype), w1 [num_local, inter,
+ * hidden]; act as in b200_act_only; hidden % 64 == 0, inter % 128 == 0. */
+int b200_moe_gemm_up_act(void* h, const void* x, const void* w1, const int32_t* offsets,
+                         const int32_t* sorted_pair, int32_t hidden, int32_t inter, int32_t num_local,
+                         int32_t top_k, int64_t x_stride, int32_t act, int32_t dtype, b200_stream_t stream);
 int b200_moe_gemm_down(void* y, const void* h, const void* w2, const int32_t* offsets,
                        const int32_t* sorted_pair, const void* topk_weights, int32_t inter,
                        int32_t hidden, int32_t num_local, int32_t top_k, int32_t dtype,
@@ -479,6 +484,16 @@ int b200_rownorm_cache(void* x, int64_t stride, const float* wq, const float* wk
 int b200_gate_prep(float* q_out, float* f_out, const void* q, int64_t q_stride, const void* f, int64_t f_stride,
                    const float* bias, const float* lower, int32_t num_tokens, int32_t n, int32_t dtype,
                    b200_stream_t stream);
+
+/* Softmax of heads that are mixed before it, over blocks of raw fp32 dot products s [entries, G, C, rep, nk] (entry:
+ * a chunk of a prompt or a sequence of a decode step; C tokens per entry; head g * rep + r; nk key columns): x_h =
+ * scale s_h - slopes[h] (pos - key); x'_h = sum_g talk[h, g] x_g; p = exp(x') / (sum over visible keys + exp(sink[h])),
+ * written in dtype over all nk columns (hidden keys 0). Positions as in b200_masked_softmax: chunk_first / chunk_lo
+ * per entry, or ctx_lens (C == 1, the columns are the last nk positions). H <= 64, (H nk + H^2) * 4 <= 200 KB. */
+int b200_mixed_softmax(void* p, const float* s, int32_t entries, int32_t tokens_per_entry, int32_t num_kv_heads,
+                       int32_t rep, int32_t nk, float scale, int32_t window, const float* slopes, const float* talk,
+                       const float* sink, const int32_t* ctx_lens, const int32_t* chunk_first,
+                       const int32_t* chunk_lo, int32_t dtype, b200_stream_t stream);
 
 /* Causal softmax attention whose heads are mixed BEFORE the softmax: s_h(i, j) = scale q_h,i.k_j - slopes[h] (i - j);
  * s'_h = sum_g talk[h, g] s_g; softmax over the visible keys with exp(sink[h]) added to the denominator. slopes,

@@ -175,6 +175,7 @@ struct MoeGemmParams {
   const void* pair_scale;      // down: routing weight of every pair, [tokens * top_k]
   int64_t a_stride;            // elements between rows of a
   int K, n_out, top_k;
+  int act;                     // up alone (mode 2): 0 silu, 1 relu, 2 gelu (tanh form), 3 squared relu
 };
 
 constexpr int kMoeStages = 4;
@@ -195,10 +196,25 @@ __device__ __forceinline__ float silu_round(float g) {
   return to_f32<T>(from_f32<T>(__fdividef(g, 1.0f + __expf(-g))));
 }
 
+// act(x) in fp32, rounded to the model dtype, for experts without a gate
+template <typename T>
+__device__ __forceinline__ float plain_act_round(float x, int act) {
+  float r;
+  if (act == 1) r = fmaxf(x, 0.f);
+  else if (act == 2) r = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  else if (act == 3) r = fmaxf(x, 0.f) * fmaxf(x, 0.f);
+  else r = __fdividef(x, 1.0f + __expf(-x));
+  return to_f32<T>(from_f32<T>(r));
+}
+
 // One pass: rows [m0, m0 + 32*MI) of expert e against the CTA's 128 weight rows, full K.
-template <typename T, bool kGateUp, int MI>
+// kMode 0: down (rows in plan order, times the routing weight); 1: SiluAndMul(gate | up), rows gathered by pair;
+// 2: act(up) alone, rows gathered by pair, 128 weight rows like down.
+template <typename T, int kMode, int MI>
 __device__ __forceinline__ void moe_gemm_pass(const MoeGemmParams& p, uint8_t* smem, const T* wbase,
                                               int row_begin, int cnt, int m0, int n0) {
+  constexpr bool kGateUp = kMode == 1;
+  constexpr bool kGather = kMode != 0;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c16 = tid & 7, rowbase = tid >> 3;
   const int KB = p.K / kMoeBK;
@@ -211,7 +227,7 @@ __device__ __forceinline__ void moe_gemm_pass(const MoeGemmParams& p, uint8_t* s
     const int r = m0 + rowbase + 32 * i;
     a_ok[i] = r < cnt;
     const int pos = row_begin + (a_ok[i] ? r : 0);
-    const int64_t src_row = kGateUp ? (int64_t)(p.sorted_pair[pos] / p.top_k) : (int64_t)pos;
+    const int64_t src_row = kGather ? (int64_t)(p.sorted_pair[pos] / p.top_k) : (int64_t)pos;
     a_src[i] = ag + src_row * p.a_stride + c16 * 8;
   }
   const T* b_src[4];
@@ -290,6 +306,14 @@ __device__ __forceinline__ void moe_gemm_pass(const MoeGemmParams& p, uint8_t* s
         const float u0 = to_f32<T>(from_f32<T>(acc[mf][1][2 * r])), u1 = to_f32<T>(from_f32<T>(acc[mf][1][2 * r + 1]));
         const uint32_t h = pack2<T>(__fmul_rn(silu_round<T>(g0), u0), __fmul_rn(silu_round<T>(g1), u1));
         *reinterpret_cast<uint32_t*>(og + pos * p.n_out + n0 + warp * 8 + 2 * t4) = h;
+      } else if (kMode == 2) {
+        // up in the model dtype (F.linear), the activation in fp32 -> dtype
+#pragma unroll
+        for (int nf = 0; nf < 2; ++nf) {
+          const float y0 = to_f32<T>(from_f32<T>(acc[mf][nf][2 * r])), y1 = to_f32<T>(from_f32<T>(acc[mf][nf][2 * r + 1]));
+          *reinterpret_cast<uint32_t*>(og + pos * p.n_out + n0 + warp * 16 + nf * 8 + 2 * t4) =
+              pack2<T>(plain_act_round<T>(y0, p.act), plain_act_round<T>(y1, p.act));
+        }
       } else {
         // expert output in the model dtype, then a dtype multiply with the routing weight
         const float sc = to_f32<T>(reinterpret_cast<const T*>(p.pair_scale)[p.sorted_pair[pos]]);
@@ -306,9 +330,10 @@ __device__ __forceinline__ void moe_gemm_pass(const MoeGemmParams& p, uint8_t* s
 
 // grid (n tiles, num_local experts); gate_up: tile = 64 gate + the 64 matching up rows of W13,
 // down: 128 rows of W2.
-template <typename T, bool kGateUp>
+template <typename T, int kMode>
 __global__ void __launch_bounds__(256, 2)
 moe_gemm_kernel(const MoeGemmParams p) {
+  constexpr bool kGateUp = kMode == 1;
   extern __shared__ __align__(1024) uint8_t moe_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(moe_smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -321,10 +346,10 @@ moe_gemm_kernel(const MoeGemmParams p) {
   const T* wbase = reinterpret_cast<const T*>(p.w) + (int64_t)e * (kGateUp ? 2 : 1) * p.n_out * p.K;
   for (int m0 = 0; m0 < cnt;) {
     if (cnt - m0 > 32) {
-      moe_gemm_pass<T, kGateUp, 2>(p, smem, wbase, row_begin, cnt, m0, n0);
+      moe_gemm_pass<T, kMode, 2>(p, smem, wbase, row_begin, cnt, m0, n0);
       m0 += 64;
     } else {
-      moe_gemm_pass<T, kGateUp, 1>(p, smem, wbase, row_begin, cnt, m0, n0);
+      moe_gemm_pass<T, kMode, 1>(p, smem, wbase, row_begin, cnt, m0, n0);
       m0 += 32;
     }
   }
@@ -382,15 +407,15 @@ moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y, const int32_t* 
 }
 
 template <typename T>
-static int moe_gemm_launch(bool gate_up, const MoeGemmParams& p, int num_local, cudaStream_t stream) {
-  auto kern = gate_up ? moe_gemm_kernel<T, true> : moe_gemm_kernel<T, false>;
-  static bool configured[2] = {false, false};
-  if (!configured[gate_up]) {
+static int moe_gemm_launch(int mode, const MoeGemmParams& p, int num_local, cudaStream_t stream) {
+  auto kern = mode == 1 ? moe_gemm_kernel<T, 1> : mode == 2 ? moe_gemm_kernel<T, 2> : moe_gemm_kernel<T, 0>;
+  static bool configured[3] = {false, false, false};
+  if (!configured[mode]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMoeSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    configured[gate_up] = true;
+    configured[mode] = true;
   }
-  const dim3 grid(p.n_out / (gate_up ? 64 : 128), num_local);
+  const dim3 grid(p.n_out / (mode == 1 ? 64 : 128), num_local);
   launch_pdl(kern, grid, dim3(256), (size_t)kMoeSmemBytes, stream, p);
   return finish_launch();
 }
@@ -458,9 +483,22 @@ extern "C" int b200_moe_gemm_gate_up(void* h, const void* x, const void* w13, co
   const int rc = moe_gemm_check(x, w13, h, offsets, sorted_pair, hidden, inter, 64, num_local, top_k,
                                 x_stride, dtype);
   if (rc != B200_OK) return rc;
-  MoeGemmParams p{x, w13, h, offsets, sorted_pair, nullptr, x_stride, hidden, inter, top_k};
-  return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(true, p, num_local, (cudaStream_t)stream)
-                                  : moe_gemm_launch<__half>(true, p, num_local, (cudaStream_t)stream);
+  MoeGemmParams p{x, w13, h, offsets, sorted_pair, nullptr, x_stride, hidden, inter, top_k, 0};
+  return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(1, p, num_local, (cudaStream_t)stream)
+                                  : moe_gemm_launch<__half>(1, p, num_local, (cudaStream_t)stream);
+}
+
+extern "C" int b200_moe_gemm_up_act(void* h, const void* x, const void* w1, const int32_t* offsets,
+                                    const int32_t* sorted_pair, int32_t hidden, int32_t inter, int32_t num_local,
+                                    int32_t top_k, int64_t x_stride, int32_t act, int32_t dtype,
+                                    b200_stream_t stream) {
+  const int rc = moe_gemm_check(x, w1, h, offsets, sorted_pair, hidden, inter, 128, num_local, top_k, x_stride,
+                                dtype);
+  if (rc != B200_OK) return rc;
+  B200_RETURN_IF(act < 0 || act > 3, B200_ERR_BAD_SHAPE);
+  MoeGemmParams p{x, w1, h, offsets, sorted_pair, nullptr, x_stride, hidden, inter, top_k, act};
+  return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(2, p, num_local, (cudaStream_t)stream)
+                                  : moe_gemm_launch<__half>(2, p, num_local, (cudaStream_t)stream);
 }
 
 extern "C" int b200_moe_gemm_down(void* y, const void* h, const void* w2, const int32_t* offsets,
@@ -471,9 +509,9 @@ extern "C" int b200_moe_gemm_down(void* y, const void* h, const void* w2, const 
                                 inter, dtype);
   if (rc != B200_OK) return rc;
   B200_RETURN_IF(!topk_weights, B200_ERR_NULL_POINTER);
-  MoeGemmParams p{h, w2, y, offsets, sorted_pair, topk_weights, inter, inter, hidden, top_k};
-  return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(false, p, num_local, (cudaStream_t)stream)
-                                  : moe_gemm_launch<__half>(false, p, num_local, (cudaStream_t)stream);
+  MoeGemmParams p{h, w2, y, offsets, sorted_pair, topk_weights, inter, inter, hidden, top_k, 0};
+  return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(0, p, num_local, (cudaStream_t)stream)
+                                  : moe_gemm_launch<__half>(0, p, num_local, (cudaStream_t)stream);
 }
 
 extern "C" int b200_moe_combine(void* out, const void* y, const int32_t* topk_ids,

@@ -12,6 +12,8 @@
 //   latent_kv_prep      RMS norm of the query latent; RMS norm of the key/value latent and rotation of the shared
 //                       rotated key, written as one cache row [latent | rotated key] (packed and/or paged).
 //   glu_clamped         min(g, L) sigmoid(alpha min(g, L)) (clamp(u, -L, L) + 1) for a gated feed-forward.
+//   masked_softmax      softmax over the visible keys of a block of fp32 scores (attention composed of library products).
+//   mixed_softmax       the same for heads that are mixed BEFORE the softmax: distance bias, [H, H] mix, mask, sink.
 //
 // All arithmetic is fp32 (angles in fp64: a position times a frequency loses digits in fp32 at long range).
 #include "seq_common.cuh"
@@ -421,9 +423,119 @@ masked_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int64_t ro
     pr[j] = from_f32<T>((j >= lo && j < hi) ? expf((sr[j] - m) * scale) * inv : 0.f);
 }
 
+// ------------------------------------------------------------------ softmax of heads that talk to each other
+// s: raw dot products fp32 [B, G, C, rep, nk] -- entry b (a chunk of a prompt, or a sequence of a decode step), kv head
+// g, token c of the entry, query head g * rep + r, key column j. One CTA per (b, c) holds the token's H x visible-keys
+// block in shared memory: x_h(j) = scale s_h(j) - slope_h (pos - key(j)); x'_h = sum_g talk[h][g] x_g; p_h = exp(x'_h) /
+// (sum_visible exp(x'_h) + exp(sink_h)), written in the element type over ALL nk columns (hidden keys 0). Positions as
+// in masked_softmax: chunks (chunk_first / chunk_lo per entry, token c at chunk_first + c) or one token per sequence
+// (ctx_lens; C == 1; the columns are the last nk positions). HM >= H bounds the per-thread column of heads.
+template <typename T, int HM>
+__global__ void __launch_bounds__(256)
+mixed_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int C, int G, int rep, int nk, float scale,
+                     int window, const float* __restrict__ slopes, const float* __restrict__ talk,
+                     const float* __restrict__ sink, const int* __restrict__ ctx_lens,
+                     const int* __restrict__ chunk_first, const int* __restrict__ chunk_lo) {
+  extern __shared__ float sm[];                       // [H][nk] then talk [H][H]
+  pdl_wait();
+  const int H = G * rep;
+  const int b = blockIdx.y, c = blockIdx.x;
+  float* stalk = sm + (size_t)H * nk;
+  int pos, key_lo;
+  if (chunk_first != nullptr) {
+    pos = chunk_first[b] + c;
+    key_lo = chunk_lo[b];
+  } else {
+    pos = ctx_lens[b] - 1;
+    key_lo = pos - nk + 1;
+  }
+  const int hi = pos < 0 ? 0 : min(nk, pos - key_lo + 1);                    // visible: columns [lo, hi)
+  int lo = max(0, -key_lo);
+  if (window > 0) lo = max(lo, pos - window + 1 - key_lo);
+  const int nv = max(0, hi - lo);
+  if (talk != nullptr)
+    for (int e = threadIdx.x; e < H * H; e += blockDim.x) stalk[e] = talk[e];
+  auto row_of = [&](int h) { return (((int64_t)b * G + h / rep) * C + c) * rep + h % rep; };
+  for (int h = 0; h < H; ++h) {
+    const float* sr = s + row_of(h) * nk;
+    const float slope = slopes != nullptr ? slopes[h] : 0.f;
+    for (int j = threadIdx.x; j < nv; j += blockDim.x)
+      sm[(size_t)h * nk + j] = sr[lo + j] * scale - slope * (float)(pos - (key_lo + lo + j));
+  }
+  __syncthreads();
+  if (talk != nullptr) {
+    for (int j = threadIdx.x; j < nv; j += blockDim.x) {                     // a thread mixes one key's column of heads
+      float v[HM];
+#pragma unroll
+      for (int g = 0; g < HM; ++g) v[g] = g < H ? sm[(size_t)g * nk + j] : 0.f;
+      for (int h = 0; h < H; ++h) {
+        const float* tr = stalk + h * H;
+        float d = 0.f;
+#pragma unroll
+        for (int g = 0; g < HM; ++g)
+          if (g < H) d += tr[g] * v[g];
+        sm[(size_t)h * nk + j] = d;
+      }
+    }
+    __syncthreads();
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nw) {
+    float* x = sm + (size_t)h * nk;
+    float m = -INFINITY;
+    for (int j = lane; j < nv; j += 32) m = fmaxf(m, x[j]);
+    m = warp_max(m);
+    const float sk = sink != nullptr ? sink[h] : -INFINITY;
+    m = fmaxf(m, sk);
+    float l = 0.f;
+    for (int j = lane; j < nv; j += 32) {
+      const float e = expf(x[j] - m);
+      x[j] = e;
+      l += e;
+    }
+    l = warp_sum(l) + (sink != nullptr ? expf(sk - m) : 0.f);
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    T* pr = p + row_of(h) * nk;
+    for (int j = lane; j < nk; j += 32) pr[j] = from_f32<T>((j >= lo && j < hi) ? x[j - lo] * inv : 0.f);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_mixed_softmax(void* p, const float* s, int32_t entries, int32_t tokens_per_entry,
+                                  int32_t num_kv_heads, int32_t rep, int32_t nk, float scale, int32_t window,
+                                  const float* slopes, const float* talk, const float* sink,
+                                  const int32_t* ctx_lens, const int32_t* chunk_first, const int32_t* chunk_lo,
+                                  int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(entries < 0 || tokens_per_entry <= 0 || num_kv_heads <= 0 || rep <= 0 || nk <= 0 || window < 0,
+                 B200_ERR_BAD_SHAPE);
+  if (entries == 0) return B200_OK;
+  B200_RETURN_IF(!p || !s || (ctx_lens == nullptr) == (chunk_first == nullptr) || (chunk_first && !chunk_lo),
+                 B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(ctx_lens && tokens_per_entry != 1, B200_ERR_BAD_SHAPE);
+  const int H = num_kv_heads * rep;
+  B200_RETURN_IF(H > 64 || entries > 65535, B200_ERR_UNSUPPORTED);
+  const size_t smem = ((size_t)H * nk + (size_t)H * H) * sizeof(float);
+  B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
+  const dim3 grid(tokens_per_entry, entries);
+#define B200_MIXSM(HMV)                                                                                              \
+  B200_DISPATCH_3(dtype, T, {                                                                                        \
+    if (smem > 48 * 1024)                                                                                            \
+      cudaFuncSetAttribute(mixed_softmax_kernel<T, HMV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    launch_pdl(mixed_softmax_kernel<T, HMV>, grid, dim3(256), smem, (cudaStream_t)stream, (T*)p, s,                  \
+               tokens_per_entry, num_kv_heads, rep, nk, scale, window, slopes, talk, sink, ctx_lens, chunk_first,    \
+               chunk_lo);                                                                                            \
+  })
+  if (H <= 4) B200_MIXSM(4);
+  else if (H <= 8) B200_MIXSM(8);
+  else if (H <= 16) B200_MIXSM(16);
+  else if (H <= 32) B200_MIXSM(32);
+  else B200_MIXSM(64);
+#undef B200_MIXSM
+  return finish_launch();
+}
 
 extern "C" int b200_masked_softmax(void* p, const float* s, int64_t rows, int32_t nk, int32_t heads,
                                    int32_t first_pos, int32_t key_lo, int32_t window, float scale,

@@ -68,6 +68,8 @@ PROTOTYPES = {
                                  c_int32, c_void_p]),
     "b200_moe_gemm_gate_up": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                         c_int32, c_int32, c_int32, c_int64, c_int32, c_void_p]),
+    "b200_moe_gemm_up_act": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                       c_int32, c_int64, c_int32, c_int32, c_void_p]),
     "b200_moe_gemm_down": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200_moe_gather_rows": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
@@ -152,6 +154,8 @@ PROTOTYPES = {
                                      c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200_gate_prep": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int32,
                                  c_int32, c_int32, c_void_p]),
+    "b200_mixed_softmax": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_float, c_int32,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
     "b200_mixed_attn": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                   c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                   c_int32, c_int32, c_int32, c_float, c_int32, c_void_p, c_void_p, c_void_p, c_int32,

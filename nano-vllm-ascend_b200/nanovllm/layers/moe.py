@@ -144,9 +144,9 @@ class TopkSoftmaxMoe(nn.Module):
     """Mixture of experts whose router is a plain linear map with a bias, computed in fp32: the ``top_k`` experts with
     the largest logits are chosen and weighted by the softmax over the chosen logits only. Experts are feed-forwards
     WITHOUT a gate, W_down act(W_up h), no biases, stacked in two tensors (``w1`` [E, inter, hidden], ``w2`` [E, hidden,
-    inter]). 16-bit models whose sizes fit the tensor-core kernels run the expert GEMMs on them (the up product through
-    the grouped tcgen05 GEMM with fp32 output, then the activation), everything else (fp32, other sizes) on the generic
-    kernels of csrc/moe_generic.cu; routing weights stay fp32 and are applied in an fp32 combine."""
+    inter]). 16-bit models whose sizes fit the tensor-core kernels run the expert GEMMs on them (ops.moe_experts_ungated:
+    the grouped tcgen05 GEMM for prompt-sized batches, the weight-streaming kernels below that), everything else (fp32,
+    other sizes) on the generic kernels of csrc/moe_generic.cu with fp32 routing weights in an fp32 combine."""
 
     def __init__(self, hidden_size: int, inter: int, num_experts: int, top_k: int, act: str = "relu2"):
         super().__init__()
@@ -159,9 +159,13 @@ class TopkSoftmaxMoe(nn.Module):
         self.w2 = nn.Parameter(torch.empty(num_experts, hidden_size, inter))
         self.w1.weight_loader = lambda p, w, e: p.data[e].copy_(w)
         self.w2.weight_loader = lambda p, w, e: p.data[e].copy_(w)
+        self.fast = True           # False: always the generic kernels
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = F.linear(x.float(), self.router)
         ids, w = ops.moe_route_topk(logits, self.router_bias, self.top_k)
         plan = ops.moe_align(ids, 0, self.num_experts)
+        if (self.fast and x.dtype != torch.float32 and self.hidden_size % 128 == 0 and self.inter % 128 == 0
+                and self.top_k <= 8 and self.num_experts <= 256):
+            return ops.moe_experts_ungated(x, self.w1, self.w2, ids, w.to(x.dtype), plan, act=self.act)
         return ops.moe_experts_generic(x, self.w1, self.w2, w, plan, act=self.act)

@@ -205,6 +205,7 @@ class MixedHeadAttention(nn.Module):
         self.k_cache = torch.tensor([])
         self.v_cache = torch.tensor([])
         self.layer_id = -1
+        self.force_generic = False                  # True: always the kernel of csrc/mixed_attn.cu
         self.step_kv = None                         # this step's (k, v) rows, kept for a borrower when no cache is bound
 
     def cache_rows(self) -> tuple[int, int]:
@@ -220,11 +221,112 @@ class MixedHeadAttention(nn.Module):
         else:
             k, v = self.kv_source.step_kv
         spans = ops.StepSpans.of(ctx)
-        kw = dict(window=self.window, slopes=self.slopes, talk=self.talk, sink=self.sink)
-        if self.k_cache.numel() > 0 and ctx.block_tables is not None:
+        paged = self.k_cache.numel() > 0 and ctx.block_tables is not None
+        sixteen = q.dtype != torch.float32 and not self.force_generic and self.num_heads <= 64
+        if (sixteen and ctx.is_prefill and ctx.host_spans is not None and ctx.max_seqlen_q >= self.PRODUCT_MIN_TOKENS):
+            out = self._prefill_by_products(q, k, v, ctx, paged)
+            if out is not None:
+                return out
+        elif (sixteen and not ctx.is_prefill and paged and self.window > 0 and
+              min(self.window, ctx.block_tables.shape[1] * ctx.block_size) <= self.DECODE_WINDOW_MAX and
+              self._fits(min(self.window, ctx.block_tables.shape[1] * ctx.block_size))):
+            return self._decode_window_by_products(q, ctx)
+        if paged:
             return ops.mixed_attn(q, self.k_cache, self.v_cache, spans, self.scale, self.num_kv_heads, self.vdim,
-                                  block_tables=ctx.block_tables, **kw)
-        return ops.mixed_attn(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, **kw)
+                                  block_tables=ctx.block_tables, **self._extras())
+        return ops.mixed_attn(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, **self._extras())
+
+    def _extras(self):
+        return dict(window=self.window, slopes=self.slopes, talk=self.talk, sink=self.sink)
+
+    def _fits(self, nk: int) -> bool:
+        """The softmax kernel keeps a token's heads x keys block (and the mixing matrix) in shared memory."""
+        H = self.num_heads
+        return (H * nk + H * H) * 4 <= ops.MIXED_SOFTMAX_SMEM
+
+    DECODE_WINDOW_MAX = 4096      # decode steps gather a window of at most this many rows per sequence
+    PRODUCT_BYTES = 512 << 20     # fp32 scores held at a time
+    PRODUCT_MIN_TOKENS = 64       # longest portion of the step from which prompts run on library products
+    PRODUCT_CHUNK = 256           # query tokens per product
+
+    def _decode_window_by_products(self, q, ctx):
+        """Decode steps inside a sliding window, 16-bit models: the last `window` cached key and value rows of every
+        sequence are gathered into dense blocks (fixed shapes: capturable in a CUDA graph); one batched library product
+        per kv head gives the raw scores of its query heads (fp32 out); the mixed softmax kernel applies scale, distance
+        bias, head mixing, mask (rows before a sequence's start, padded graph rows) and sink; one batched product with
+        the value rows. Without a window the kernel of csrc/mixed_attn.cu reads the cache through the block table."""
+        B, H, d = q.shape
+        G, dv, bs = self.num_kv_heads, self.vdim, ctx.block_size
+        rep = H // G
+        W = min(self.window, ctx.block_tables.shape[1] * bs)                 # no sequence holds more rows than its table
+        slots = ctx.scratch.get(("window rows", W))                          # the same for every layer of the step
+        if slots is None:
+            pos = ctx.context_lens.long() - 1                                # -1 on padded rows
+            j = (pos[:, None] - (W - 1) + torch.arange(W, device=q.device)).clamp(min=0)
+            blocks = ctx.block_tables.gather(1, j // bs).clamp(min=0).long()
+            slots = ctx.scratch[("window rows", W)] = (blocks * bs + j % bs).view(-1)
+        krows = self.k_cache.view(-1, G * d)[slots].view(B, W, G, d).permute(0, 2, 3, 1).reshape(B * G, d, W)
+        vrows = self.v_cache.view(-1, G * dv)[slots].view(B, W, G, dv).permute(0, 2, 1, 3).reshape(B * G, W, dv)
+        scores = torch.bmm(q.reshape(B * G, rep, d), krows, out_dtype=torch.float32)          # [B * G, rep, W]
+        p = ops.mixed_softmax(scores.view(B, G, 1, rep, W), self.scale, self.window, q.dtype, self.slopes, self.talk,
+                              self.sink, ctx_lens=ctx.context_lens)
+        return torch.bmm(p.view(B * G, rep, W), vrows).reshape(B, H * dv)
+
+    def _prefill_by_products(self, q, k, v, ctx, paged):
+        """Prompt portions of 16-bit models on the tensor cores, all chunks of the step at once: gather the chunks' query
+        rows and key/value ranges; the raw scores of every kv head's query heads against its keys as one batched library
+        product with fp32 output; the mixed softmax kernel (scale, distance bias, head mixing, mask, sink; fp32 in,
+        16-bit probabilities out); one batched product with the values. Portions shorter than PRODUCT_MIN_TOKENS beside
+        long ones run on the kernel of csrc/mixed_attn.cu; so does the whole step (None is returned) when a token's
+        heads x keys block would not fit the softmax kernel's shared memory."""
+        T, H, d = q.shape
+        G, dv, CH = self.num_kv_heads, self.vdim, self.PRODUCT_CHUNK
+        rep = H // G
+        key = ("prompt plan", self.window, CH, self.PRODUCT_MIN_TOKENS, paged)
+        plan = ctx.scratch.get(key)
+        if plan is None:
+            plan = ctx.scratch[key] = prompt_chunk_plan(ctx, paged, q.device, CH, self.window, self.PRODUCT_MIN_TOKENS)
+        NC = plan["chunks"]
+        if NC and not self._fits(plan["NK"]):
+            return None
+        out = torch.empty(T, H * dv, dtype=q.dtype, device=q.device)
+        for s, q0, ql, kl in plan["short"]:
+            sub = ops.StepSpans(torch.tensor([0, ql], dtype=torch.int32, device=q.device),
+                                torch.tensor([0, kl], dtype=torch.int32, device=q.device), None, ql)
+            if paged:
+                out[q0:q0 + ql] = ops.mixed_attn(q[q0:q0 + ql], self.k_cache, self.v_cache, sub, self.scale, G, dv,
+                                                 block_tables=ctx.block_tables[s:s + 1], **self._extras())
+            else:
+                out[q0:q0 + ql] = ops.mixed_attn(q[q0:q0 + ql], k[q0:q0 + ql], v[q0:q0 + ql], sub, self.scale, G, dv,
+                                                 **self._extras())
+        if NC == 0:
+            return out
+        NK = plan["NK"]
+        flat_k = self.k_cache.view(-1, G * d) if paged else k.reshape(T, G * d)
+        flat_v = self.v_cache.view(-1, G * dv) if paged else v.reshape(T, G * dv)
+        per = max(1, min(256, self.PRODUCT_BYTES // (CH * H * NK * 4)))      # chunks per launch: bounded score memory
+        for g0 in range(0, NC, per):
+            g1 = min(NC, g0 + per)
+            n = g1 - g0
+            kslots = plan["kslots"][g0 * NK:g1 * NK]
+            kt = flat_k[kslots].view(n, NK, G, d).permute(0, 2, 3, 1).reshape(n * G, d, NK)
+            vv = flat_v[kslots].view(n, NK, G, dv).permute(0, 2, 1, 3).reshape(n * G, NK, dv)
+            run = plan["run"]
+            qs = q[run + g0 * CH:run + g1 * CH] if run is not None else q[plan["qrows"][g0 * CH:g1 * CH]]
+            qs = qs.reshape(n, CH, G, rep, d).permute(0, 2, 1, 3, 4).reshape(n * G, CH * rep, d)
+            scores = torch.bmm(qs, kt, out_dtype=torch.float32)                                 # [n * G, CH * rep, NK]
+            p = ops.mixed_softmax(scores.view(n, G, CH, rep, NK), self.scale, self.window, q.dtype, self.slopes,
+                                  self.talk, self.sink, chunks=(plan["first"][g0:g1], plan["lo"][g0:g1]))
+            o = torch.bmm(p.view(n * G, CH * rep, NK), vv)                                      # [n * G, CH * rep, dv]
+            o = o.view(n, G, CH, rep, dv).permute(0, 2, 1, 3, 4).reshape(n * CH, H * dv)
+            if run is not None:
+                out[run + g0 * CH:run + g1 * CH] = o
+            elif plan["full"]:
+                out[plan["qrows"][g0 * CH:g1 * CH]] = o
+            else:
+                sel = (plan["src"] >= g0 * CH) & (plan["src"] < g1 * CH)
+                out[plan["dst"][sel]] = o[plan["src"][sel] - g0 * CH]
+        return out
 
 
 class DeltaRule(nn.Module):
@@ -266,6 +368,53 @@ class Rotary:
         """x [T, heads, width] view -> rotated (and scaled) copy, see ops.rotary_heads."""
         return ops.rotary_heads(x, positions, x.shape[1], x.shape[2], self.dims, self.base, self.interleaved, out=out,
                                 out_f32=out_f32, split=split, scale_lo=scale_lo, scale_hi=scale_hi)
+
+
+def prompt_chunk_plan(ctx, paged, device, chunk: int, window: int, min_tokens: int):
+    """Index tensors of the step's prompt chunks, built once per pass and shared by the layers: every span of at
+    least `min_tokens` tokens is cut into chunks of `chunk` query tokens; all chunks see a key range of
+    the same length NK (a multiple of 128 that covers the widest visible range; what lies before a sequence's
+    start or outside a row's window is hidden by the softmax kernel)."""
+    import numpy as np
+    CH, W, bs = chunk, window, ctx.block_size
+    chunks, short = [], []                      # (sequence, first token row, tokens, first position)
+    for s, (q0, ql, kl) in enumerate(ctx.host_spans):
+        if ql < min_tokens:
+            short.append((s, q0, ql, kl))
+            continue
+        for c0 in range(0, ql, CH):
+            chunks.append((s, q0 + c0, min(CH, ql - c0), kl - ql + c0))
+    plan = {"short": short, "chunks": len(chunks)}
+    if not chunks:
+        return plan
+    seq = np.array([c[0] for c in chunks])
+    row0 = np.array([c[1] for c in chunks])
+    n = np.array([c[2] for c in chunks])
+    pos0 = np.array([c[3] for c in chunks])
+    hi = pos0 + n                                # keys of a chunk end at its last token
+    vis_lo = np.maximum(0, pos0 - W + 1) if W else np.zeros_like(pos0)
+    NK = int(-(-int((hi - vis_lo).max()) // 128) * 128)
+    lo = hi - NK                                 # may be negative: those columns repeat row 0 and are hidden
+    dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dt).to(device, non_blocking=True)
+    tok = np.arange(CH)[None, :]
+    qrows = row0[:, None] + np.minimum(tok, n[:, None] - 1)           # rows past a chunk's end repeat its last token
+    kpos = np.maximum(lo[:, None] + np.arange(NK)[None, :], 0)
+    kpos_d = dev(kpos, torch.int64)
+    if paged:
+        tables = ctx.block_tables[dev(seq, torch.int64)]               # [chunks, blocks]
+        kslots = tables.gather(1, kpos_d // bs).long() * bs + kpos_d % bs
+    else:                                        # no cache bound: a span's keys are this step's rows
+        span_row0 = np.array([ctx.host_spans[c[0]][0] for c in chunks])
+        kslots = kpos_d + dev(span_row0, torch.int64)[:, None]
+    valid = tok < n[:, None]                     # [chunks, CH]
+    flatq = qrows.reshape(-1)
+    # chunks that are all full and follow each other in the packed batch need no gather of query rows
+    plan["run"] = int(flatq[0]) if bool(valid.all()) and bool((np.diff(flatq) == 1).all()) else None
+    plan.update(NK=NK, qrows=dev(qrows.reshape(-1), torch.int64), kslots=kslots.reshape(-1),
+                first=dev(pos0, torch.int32), lo=dev(lo, torch.int32),
+                src=dev(np.nonzero(valid.reshape(-1))[0], torch.int64), dst=dev(qrows[valid], torch.int64),
+                full=bool(valid.all()))
+    return plan
 
 
 class LatentAttention(nn.Module):
@@ -352,50 +501,7 @@ class LatentAttention(nn.Module):
     PRODUCT_CHUNK = 512           # query tokens per product
 
     def _prompt_plan(self, ctx, paged, device):
-        """Index tensors of the step's prompt chunks, built once per pass and shared by the layers: every span of at
-        least PRODUCT_MIN_TOKENS tokens is cut into chunks of PRODUCT_CHUNK query tokens; all chunks see a key range of
-        the same length NK (a multiple of 128 that covers the widest visible range; what lies before a sequence's
-        start or outside a row's window is hidden by the softmax kernel)."""
-        import numpy as np
-        CH, W, bs = self.PRODUCT_CHUNK, self.window, ctx.block_size
-        chunks, short = [], []                      # (sequence, first token row, tokens, first position)
-        for s, (q0, ql, kl) in enumerate(ctx.host_spans):
-            if ql < self.PRODUCT_MIN_TOKENS:
-                short.append((s, q0, ql, kl))
-                continue
-            for c0 in range(0, ql, CH):
-                chunks.append((s, q0 + c0, min(CH, ql - c0), kl - ql + c0))
-        plan = {"short": short, "chunks": len(chunks)}
-        if not chunks:
-            return plan
-        seq = np.array([c[0] for c in chunks])
-        row0 = np.array([c[1] for c in chunks])
-        n = np.array([c[2] for c in chunks])
-        pos0 = np.array([c[3] for c in chunks])
-        hi = pos0 + n                                # keys of a chunk end at its last token
-        vis_lo = np.maximum(0, pos0 - W + 1) if W else np.zeros_like(pos0)
-        NK = int(-(-int((hi - vis_lo).max()) // 128) * 128)
-        lo = hi - NK                                 # may be negative: those columns repeat row 0 and are hidden
-        dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dt).to(device, non_blocking=True)
-        tok = np.arange(CH)[None, :]
-        qrows = row0[:, None] + np.minimum(tok, n[:, None] - 1)           # rows past a chunk's end repeat its last token
-        kpos = np.maximum(lo[:, None] + np.arange(NK)[None, :], 0)
-        kpos_d = dev(kpos, torch.int64)
-        if paged:
-            tables = ctx.block_tables[dev(seq, torch.int64)]               # [chunks, blocks]
-            kslots = tables.gather(1, kpos_d // bs).long() * bs + kpos_d % bs
-        else:                                        # no cache bound: a span's keys are this step's rows
-            span_row0 = np.array([ctx.host_spans[c[0]][0] for c in chunks])
-            kslots = kpos_d + dev(span_row0, torch.int64)[:, None]
-        valid = tok < n[:, None]                     # [chunks, CH]
-        flatq = qrows.reshape(-1)
-        # chunks that are all full and follow each other in the packed batch need no gather of query rows
-        plan["run"] = int(flatq[0]) if bool(valid.all()) and bool((np.diff(flatq) == 1).all()) else None
-        plan.update(NK=NK, qrows=dev(qrows.reshape(-1), torch.int64), kslots=kslots.reshape(-1),
-                    first=dev(pos0, torch.int32), lo=dev(lo, torch.int32),
-                    src=dev(np.nonzero(valid.reshape(-1))[0], torch.int64), dst=dev(qrows[valid], torch.int64),
-                    full=bool(valid.all()))
-        return plan
+        return prompt_chunk_plan(ctx, paged, device, self.PRODUCT_CHUNK, self.window, self.PRODUCT_MIN_TOKENS)
 
     def _prefill_by_products(self, qx, kc, ctx, paged):
         """Prompt portions of 16-bit models on the tensor cores, all chunks of the step at once: gather the chunks'

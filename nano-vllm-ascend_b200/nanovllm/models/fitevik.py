@@ -199,6 +199,9 @@ class FitevikForCausalLM(nn.Module):
         return out
 
     def forward(self, input_ids, positions):
+        # index tensors that the layers share live for ONE pass: a context may see several passes (an eager pass, then
+        # the capture of a CUDA graph), and what an earlier pass computed is neither current nor part of the graph
+        get_context().scratch.clear()
         dtype = self.embed_tokens.weight.dtype
         T, W = input_ids.shape[0], self.spec.hidden_size
         x = torch.empty(T, W, dtype=torch.float32, device=input_ids.device)            # the residual stream

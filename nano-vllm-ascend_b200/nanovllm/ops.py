@@ -544,6 +544,50 @@ def _moe_expert_gemms_umma(x, w13, w2, topk_weights, plan: MoePlan) -> torch.Ten
     return y
 
 
+def moe_experts_ungated(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_ids: torch.Tensor,
+                        topk_weights: torch.Tensor, plan: MoePlan, act: str = "relu2") -> torch.Tensor:
+    """Experts WITHOUT a gate on the tensor-core kernels, down(act(up x)) and the per-token combine, 16-bit models:
+    x [T, hidden]; w1 [E, inter, hidden]; w2 [E, hidden, inter]; topk_weights [T, k] in x's dtype. Prompt-sized
+    batches gather their rows and run both products on the grouped tcgen05 GEMM (the activation between them);
+    smaller ones run on the weight-streaming kernels (the activation is the up product's epilogue).
+    hidden % 128 == 0, inter % 128 == 0."""
+    _need_cuda(x, w1, w2, topk_ids, topk_weights)
+    T, hidden = x.shape
+    E, inter, h2 = w1.shape
+    if h2 != hidden or w2.shape != (E, hidden, inter) or E != plan.num_local:
+        raise ValueError("expert weight shapes do not match")
+    if not (w1.is_contiguous() and w2.is_contiguous() and topk_weights.is_contiguous()):
+        raise ValueError("expert weights / routing weights must be contiguous")
+    if x.stride(1) != 1 or x.dtype != w1.dtype or x.dtype != w2.dtype or x.dtype != topk_weights.dtype:
+        raise ValueError("x must be row-major and share its dtype with the weights")
+    k = plan.top_k
+    pairs = T * k
+    lib = _C.load()
+    h = torch.empty(pairs, inter, dtype=x.dtype, device=x.device)
+    y = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
+    if _MOE_BIG_GEMM != "stream" and pairs >= _MOE_BIG_GEMM_ROWS * E:
+        xs = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
+        _C.check(lib.b200_moe_gather_rows(xs.data_ptr(), x.data_ptr(), plan.offsets.data_ptr(),
+                                          plan.sorted_pair.data_ptr(), pairs, E, k, hidden,
+                                          x.stride(0) if T > 1 else hidden, _dt(x), _stream()), "b200_moe_gather_rows")
+        _C.check(lib.b200_moe_gemm_down_umma(h.data_ptr(), xs.data_ptr(), w1.data_ptr(), plan.offsets.data_ptr(), None,
+                                             None, pairs, hidden, inter, E, _dt(x), _stream()),
+                 "b200_moe_gemm_down_umma (up)")
+        h = act_only(h, act)
+        _C.check(lib.b200_moe_gemm_down_umma(y.data_ptr(), h.data_ptr(), w2.data_ptr(), plan.offsets.data_ptr(),
+                                             plan.sorted_pair.data_ptr(), topk_weights.data_ptr(), pairs, inter,
+                                             hidden, E, _dt(x), _stream()), "b200_moe_gemm_down_umma")
+        return _moe_combine(lib, y, topk_ids, plan, T, hidden, None, x)
+    _C.check(lib.b200_moe_gemm_up_act(h.data_ptr(), x.data_ptr(), w1.data_ptr(), plan.offsets.data_ptr(),
+                                      plan.sorted_pair.data_ptr(), hidden, inter, E, k,
+                                      x.stride(0) if T > 1 else hidden, _PLAIN_ACTS[act], _dt(x), _stream()),
+             "b200_moe_gemm_up_act")
+    _C.check(lib.b200_moe_gemm_down(y.data_ptr(), h.data_ptr(), w2.data_ptr(), plan.offsets.data_ptr(),
+                                    plan.sorted_pair.data_ptr(), topk_weights.data_ptr(), inter, hidden, E, k,
+                                    _dt(x), _stream()), "b200_moe_gemm_down")
+    return _moe_combine(lib, y, topk_ids, plan, T, hidden, None, x)
+
+
 def _moe_expert_gemms_library(x, w13, w2, topk_weights, plan: MoePlan) -> torch.Tensor:
     k = plan.top_k
     pair = plan.sorted_pair.long()                    # tail entries are 0: harmless rows, never combined
@@ -1078,6 +1122,36 @@ def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype, ctx_l
     _C.check(_C.load().b200_masked_softmax(p.data_ptr(), scores.data_ptr(), rows, nk, int(heads), int(first_pos),
                                            int(key_lo), int(window), float(scale), _ptr(ctx_lens), _ptr(cf), _ptr(cl),
                                            int(per), _DT3[dtype], _stream()), "b200_masked_softmax")
+    return p
+
+
+MIXED_SOFTMAX_SMEM = 200 * 1024      # a token's heads x visible keys block (+ the mixing matrix) lives in shared memory
+
+
+def mixed_softmax(scores, scale, window, dtype, slopes=None, talk=None, sink=None, ctx_lens=None, chunks=None):
+    """scores fp32 [entries, G, C, rep, nk] (raw dot products; entry = a chunk of a prompt or a sequence of a decode step,
+    C tokens per entry, head g * rep + r) -> probabilities of the same shape in `dtype` for heads that are mixed before the
+    softmax: x_h = scale s_h - slopes[h] (pos - key), x'_h = sum_g talk[h, g] x_g, softmax over the visible keys with
+    exp(sink[h]) in the denominator. chunks = (first int32 [entries], lo int32 [entries]): token c of entry b sits at
+    position first[b] + c, column j is the key at position lo[b] + j; ctx_lens int32 [entries] (C == 1): the token sits at
+    ctx_lens - 1 and the columns are the last nk positions. Visibility as in masked_softmax."""
+    _need_cuda(scores, slopes, talk, sink, ctx_lens)
+    _f32(slopes, talk, sink)
+    if scores.dtype != torch.float32 or not scores.is_contiguous() or scores.dim() != 5:
+        raise TypeError("scores are a contiguous fp32 [entries, G, C, rep, nk] tensor")
+    B, G, C, rep, nk = scores.shape
+    cf = cl = None
+    if chunks is not None:
+        cf, cl = chunks
+        _need_cuda(cf, cl)
+        if cf.dtype != torch.int32 or cl.dtype != torch.int32 or cf.numel() != B or cl.numel() != B:
+            raise TypeError("chunks: int32 first / lo per entry")
+    elif ctx_lens is None or ctx_lens.dtype != torch.int32 or not ctx_lens.is_contiguous() or ctx_lens.numel() != B or C != 1:
+        raise TypeError("give chunks, or contiguous int32 ctx_lens [entries] with one token per entry")
+    p = torch.empty(scores.shape, dtype=dtype, device=scores.device)
+    _C.check(_C.load().b200_mixed_softmax(p.data_ptr(), scores.data_ptr(), B, C, G, rep, nk, float(scale), int(window),
+                                          _ptr(slopes), _ptr(talk), _ptr(sink), _ptr(ctx_lens), _ptr(cf), _ptr(cl),
+                                          _DT3[dtype], _stream()), "b200_mixed_softmax")
     return p
 
 

@@ -631,3 +631,105 @@ def test_norm_per_head_without_a_gate(H, dv):
     assert float((got.cpu().to(F64) - want).abs().max()) < 1e-5
     gb = ops.gated_norm(_dev(y.view(13, -1)), None, _dev(w.repeat(H)), 1e-5, groups=H, dtype=torch.bfloat16)
     assert gb.dtype == torch.bfloat16 and float((gb.cpu().to(F64) - want).abs().max()) < 0.05
+
+
+def _mixed_module(H, G, d, dv, scale, window, seed):
+    from nanovllm.layers.seq_mixers import MixedHeadAttention
+    g = torch.Generator().manual_seed(seed)
+    attn = MixedHeadAttention(H, G, d, dv, scale, window=window, slope_base=8.0).cuda()
+    talk = torch.eye(H, dtype=F64) + 0.2 * torch.randn(H, H, generator=g, dtype=F64)
+    sink = torch.randn(H, generator=g, dtype=F64)
+    attn.talk.data.copy_(talk)
+    attn.sink.data.copy_(sink)
+    return attn, talk, sink
+
+
+def test_prompts_on_library_products():
+    """Prompt portions of a 16-bit model run as library products around the mixed softmax kernel: a 150-token portion
+    that continues 60 cached tokens (three query chunks of 64, key ranges that start inside the window), a second whole
+    sequence and a short portion beside them (which runs on the kernel), over a shuffled block table; a standout key
+    at the window's edge of a query in the second chunk; grouped heads with a value size other than the key size."""
+    from nanovllm.utils.context import get_context, reset_context, set_context
+    dtype, window, H, G, d, dv, bs = torch.bfloat16, 19, 6, 2, 24, 20, 16
+    lens, starts = [210, 100, 30], [60, 0, 21]                # tokens in all, tokens already cached
+    star_q, star_h = 140, 4
+    attn, talk, sink = _mixed_module(H, G, d, dv, 0.3, window, 1)
+    attn.PRODUCT_CHUNK = 64
+    cases = [_attn_case(n, H, G, d, dv, 30 + i, dtype, star=(star_q, star_q - window + 1, star_h) if i == 0 else None)
+             for i, n in enumerate(lens)]
+    wants = [O.mixed_head_attention(q[s:], k, v, 0.3, window, talk, sink, O.head_slopes(H), first_pos=s)
+             for (q, k, v), s in zip(cases, starts)]
+    assert float(wants[0][star_q - starts[0], star_h].mean()) > 2.0
+    nb = sum(-(-n // bs) for n in lens)
+    order = list(range(nb))
+    random.Random(3).shuffle(order)
+    attn.k_cache = torch.zeros(nb + 1, bs, G * d, dtype=dtype, device="cuda")
+    attn.v_cache = torch.zeros(nb + 1, bs, G * dv, dtype=dtype, device="cuda")
+    tables, at = [], 0
+    for (q, k, v), n in zip(cases, lens):
+        blocks = order[at:at + -(-n // bs)]
+        at += len(blocks)
+        tables.append(blocks + [-1] * (14 - len(blocks)))
+        for j in range(n):
+            attn.k_cache[blocks[j // bs], j % bs] = k[j].reshape(-1).to(dtype)
+            attn.v_cache[blocks[j // bs], j % bs] = v[j].reshape(-1).to(dtype)
+    q_lens = [n - s for n, s in zip(lens, starts)]
+    cu_q = [0] + list(torch.tensor(q_lens).cumsum(0).tolist())
+    cu_k = [0] + list(torch.tensor(lens).cumsum(0).tolist())
+    dev_i32 = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    qx = torch.cat([c[0][s:] for c, s in zip(cases, starts)]).to(dtype).cuda()
+    want = torch.cat([w.view(-1, H * dv) for w in wants])
+    set_context(True, cu_seqlens_q=dev_i32(cu_q), cu_seqlens_k=dev_i32(cu_k), max_seqlen_q=max(q_lens),
+                max_seqlen_k=max(lens), block_tables=dev_i32(tables), block_size=bs,
+                host_spans=[(cu_q[i], q_lens[i], lens[i]) for i in range(3)])
+    try:
+        got = attn._prefill_by_products(qx, None, None, get_context(), True).cpu().to(F64)
+        through = attn(qx).cpu().to(F64)                      # the module takes the same path by itself
+        attn.force_generic = True
+        plain = attn(qx).cpu().to(F64)
+    finally:
+        reset_context()
+    assert float((got - want).abs().max()) < 3e-2 and torch.equal(got, through)
+    assert float((plain - want).abs().max()) < 3e-2
+    row = star_q - starts[0]
+    assert float(got.view(-1, H, dv)[row, star_h].mean()) > 2.0 > float(got.view(-1, H, dv)[row + 1, star_h].mean())
+
+
+@pytest.mark.parametrize("window", [19, 200])
+def test_decode_rows_inside_a_window_on_library_products(window):
+    """Decode steps of a 16-bit model gather each sequence's last `window` key and value rows: sequences shorter than
+    the window, exactly at it, with a standout key just inside and just outside, and a padded row (0 keys) in one
+    launch; a window wider than what a block table can hold (200 > 5 blocks of 16) gathers the table's capacity."""
+    from nanovllm.utils.context import get_context, reset_context, set_context
+    dtype, H, G, d, dv, bs, star = torch.bfloat16, 4, 2, 16, 24, 16, 37
+    attn, talk, sink = _mixed_module(H, G, d, dv, 0.3, window, 2)
+    q, k, v = _attn_case(80, H, G, d, dv, 40, dtype)
+    at = [4, 18, 19, star + 18, star + 19, 79]                                      # positions of the decoded tokens
+    for i in (star + 18, star + 19):                                                # both queries point at the star key
+        q[i, 1] = 6.0 * k[star, 0] / k[star, 0].norm()
+    k[star, 0] = 6.0 * k[star, 0] / k[star, 0].norm()
+    v[star, 0] = 5.0
+    q, k, v = (x.to(dtype).to(F64) for x in (q, k, v))
+    want = O.mixed_head_attention(q, k, v, 0.3, window, talk, sink, O.head_slopes(H))
+    table = [7, 2, 5, 0, 3]
+    attn.k_cache = torch.zeros(9, bs, G * d, dtype=dtype, device="cuda")
+    attn.v_cache = torch.zeros(9, bs, G * dv, dtype=dtype, device="cuda")
+    for j in range(80):
+        attn.k_cache[table[j // bs], j % bs] = k[j].reshape(-1).to(dtype)
+        attn.v_cache[table[j // bs], j % bs] = v[j].reshape(-1).to(dtype)
+    ctx_lens = [p + 1 for p in at] + [0]
+    qx = torch.cat([q[at], torch.zeros(1, H, d, dtype=F64)]).to(dtype).cuda()
+    tables = torch.tensor([table] * 6 + [[-1] * 5], dtype=torch.int32).cuda()
+    set_context(False, context_lens=torch.tensor(ctx_lens, dtype=torch.int32).cuda(), block_tables=tables, block_size=bs)
+    try:
+        got = attn._decode_window_by_products(qx, get_context()).cpu().to(F64).view(-1, H, dv)
+        through = attn(qx).cpu().to(F64).view(-1, H, dv)
+        attn.force_generic = True
+        plain = attn(qx).cpu().to(F64).view(-1, H, dv)
+    finally:
+        reset_context()
+    assert float((got[:6] - want[at]).abs().max()) < 3e-2 and torch.equal(got, through)
+    assert float((plain[:6] - want[at]).abs().max()) < 3e-2
+    assert float(got[6].abs().max()) == 0.0
+    if window == 19:
+        assert float(got[3, 1].mean()) > 2.0 > float(got[4, 1].mean())
