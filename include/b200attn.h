@@ -489,7 +489,9 @@ int b200_gate_prep(float* q_out, float* f_out, const void* q, int64_t q_stride, 
  * a chunk of a prompt or a sequence of a decode step; C tokens per entry; head g * rep + r; nk key columns): x_h =
  * scale s_h - slopes[h] (pos - key); x'_h = sum_g talk[h, g] x_g; p = exp(x') / (sum over visible keys + exp(sink[h])),
  * written in dtype over all nk columns (hidden keys 0). Positions as in b200_masked_softmax: chunk_first / chunk_lo
- * per entry, or ctx_lens (C == 1, the columns are the last nk positions). H <= 64, (H nk + H^2) * 4 <= 200 KB. */
+ * per entry, or ctx_lens (C == 1, the columns are the last nk positions). H <= 64; a token's heads x visible keys
+ * block (at most `window` keys, else nk) lives in shared memory: (H min(nk, window) + H H') * 4 <= 200 KB, H' = H
+ * rounded up to a power of two. */
 int b200_mixed_softmax(void* p, const float* s, int32_t entries, int32_t tokens_per_entry, int32_t num_kv_heads,
                        int32_t rep, int32_t nk, float scale, int32_t window, const float* slopes, const float* talk,
                        const float* sink, const int32_t* ctx_lens, const int32_t* chunk_first,

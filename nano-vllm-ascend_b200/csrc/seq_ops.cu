@@ -635,6 +635,86 @@ norm_residual_kernel(T* __restrict__ h, float* __restrict__ res, const T* __rest
   }
 }
 
+// 16-byte form (hidden % 8 == 0, hidden <= 8 * 256 * kResVecs): a thread keeps its 8-element vectors in registers,
+// the row is read once; mean and variance from one pass over registers each.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_residual_vec_kernel(T* __restrict__ h, float* __restrict__ res, const T* __restrict__ y,
+                         const int64_t* __restrict__ y_index, int64_t y_rows, const T* __restrict__ y2,
+                         const int64_t* __restrict__ y2_index, int64_t y2_rows, const float* __restrict__ w,
+                         const float* __restrict__ b, float eps, float offset, int kind, int accumulate, int hidden) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int nvec = hidden / 8;
+  const int64_t r = blockIdx.x;
+  int64_t iy = y_index != nullptr ? y_index[r] : r;
+  if (y_index != nullptr) iy = iy < 0 ? 0 : (iy >= y_rows ? y_rows - 1 : iy);
+  const T* yr = y + iy * hidden;
+  const T* y2r = nullptr;
+  if (y2 != nullptr) {
+    int64_t i2 = y2_index != nullptr ? y2_index[r] : r;
+    if (y2_index != nullptr) i2 = i2 < 0 ? 0 : (i2 >= y2_rows ? y2_rows - 1 : i2);
+    y2r = y2 + i2 * hidden;
+  }
+  float val[kResVecs][8];
+  float s1 = 0.f;
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      load8<T>(yr + vi * 8, val[n]);
+      if (y2r != nullptr) {
+        float t[8];
+        load8<T>(y2r + vi * 8, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) val[n][e] += t[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s1 += kind == 0 ? val[n][e] : val[n][e] * val[n][e];
+    }
+  }
+  s1 = cta_sum(s1, red) / (float)hidden;
+  float mean = 0.f, rstd;
+  if (kind == 0) {
+    mean = s1;
+    float sq = 0.f;
+#pragma unroll
+    for (int n = 0; n < kResVecs; ++n) {
+      const int vi = threadIdx.x + n * blockDim.x;
+      if (vi < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = val[n][e] - mean;
+          sq += d * d;
+        }
+      }
+    }
+    rstd = 1.0f / sqrtf(cta_sum(sq, red) / (float)hidden + eps);
+  } else {
+    rstd = 1.0f / sqrtf(s1 + eps);
+  }
+  float* rr = res + r * hidden;
+  T* hr = h != nullptr ? h + r * hidden : nullptr;
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      float wv[8], bv[8], ov[8];
+      load8<float>(w + vi * 8, wv);
+      if (kind == 0 && b != nullptr) load8<float>(b + vi * 8, bv);
+      if (accumulate) load8<float>(rr + vi * 8, ov);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float nrm = kind == 0 ? (val[n][e] - mean) * rstd * wv[e] + (b != nullptr ? bv[e] : 0.f)
+                                    : val[n][e] * rstd * (offset + wv[e]);
+        ov[e] = accumulate ? ov[e] + nrm : nrm;
+      }
+      store8<float>(rr + vi * 8, ov);
+      if (hr != nullptr) store8<T>(hr + vi * 8, ov);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ q / k RMS norm over the whole projection + K/V scatter
 // One CTA per (token, part): part 0 = the nq query columns, 1 = the nk key columns, 2 = the nv value columns of row
 // x [nq | nk | nv]. q and k are divided by the root mean square of ALL their columns (every head at once), times a
@@ -673,6 +753,54 @@ rownorm_cache_kernel(T* __restrict__ x, int64_t stride, const float* __restrict_
     const T v = from_f32<T>(to_f32<T>(p[i]) * rstd * w[i]);
     p[i] = v;
     if (dst != nullptr) dst[i] = v;
+  }
+}
+
+// 16-byte form (nq, nk, nv, stride % 8 == 0): ONE WARP per (token, part), 8 per CTA -- a part is a few hundred to a few
+// thousand elements, too little for a CTA and its barriers. Two passes over the part (the second is served by L1), sums
+// by shuffles.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rownorm_cache_vec_kernel(T* __restrict__ x, int64_t stride, const float* __restrict__ wq, const float* __restrict__ wk,
+                         float eps, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
+                         int slot_pairs, int block_size, int num_tokens, int parts, int nq, int nk, int nv) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= (int64_t)num_tokens * parts) return;
+  const int64_t t = unit / parts;
+  const int part = (int)(unit % parts);
+  int64_t slot = -1;
+  if (k_cache != nullptr && part > 0)
+    slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+  T* row = x + t * stride;
+  if (part == 2) {
+    if (slot < 0) return;
+    const uint4* src = reinterpret_cast<const uint4*>(row + nq + nk);
+    uint4* dst = reinterpret_cast<uint4*>(v_cache + slot * nv);
+    for (int i = lane; i < nv * (int)sizeof(T) / 16; i += 32) dst[i] = src[i];
+    return;
+  }
+  const int n = part == 0 ? nq : nk, nvec = n / 8;
+  T* p = row + (part == 0 ? 0 : nq);
+  const float* w = part == 0 ? wq : wk;
+  float ss = 0.f;
+  for (int vi = lane; vi < nvec; vi += 32) {
+    float v[8];
+    load8<T>(p + vi * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+  T* dst = (part == 1 && slot >= 0) ? k_cache + slot * nk : nullptr;
+  for (int vi = lane; vi < nvec; vi += 32) {
+    float v[8], wv[8];
+    load8<T>(p + vi * 8, v);
+    load8<float>(w + vi * 8, wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= rstd * wv[e];
+    store8<T>(p + vi * 8, v);
+    if (dst != nullptr) store8<T>(dst + vi * 8, v);
   }
 }
 
@@ -900,6 +1028,14 @@ extern "C" int b200_norm_residual(void* h, float* residual, const void* y, const
   B200_RETURN_IF((y_index && y_rows <= 0) || (y2 && y2_index && y2_rows <= 0), B200_ERR_BAD_SHAPE);
   const size_t smem = (size_t)hidden * sizeof(float);
   B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
+  if (hidden % 8 == 0 && hidden <= 8 * 256 * kResVecs && aligned16(residual) && aligned16(y) && aligned16(w) &&
+      (!b || aligned16(b)) && (!y2 || aligned16(y2)) && (!h || aligned16(h))) {
+    const int threads = hidden / 8 >= 256 ? 256 : ((hidden / 8 + 31) / 32) * 32;
+    B200_DISPATCH_3(dtype, T, launch_pdl(norm_residual_vec_kernel<T>, dim3(rows), dim3(threads), 0,
+                                         (cudaStream_t)stream, (T*)h, residual, (const T*)y, y_index, y_rows,
+                                         (const T*)y2, y2_index, y2_rows, w, b, eps, offset, kind, accumulate, hidden));
+    return finish_launch();
+  }
   B200_DISPATCH_3(dtype, T, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(norm_residual_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -920,6 +1056,15 @@ extern "C" int b200_rownorm_cache(void* x, int64_t stride, const float* wq, cons
                  B200_ERR_NULL_POINTER);
   B200_RETURN_IF(k_cache && (nk <= 0 || nv <= 0), B200_ERR_BAD_SHAPE);
   const dim3 grid(num_tokens, nk > 0 ? (k_cache ? 3 : 2) : 1);
+  if (nq % 8 == 0 && nk % 8 == 0 && nv % 8 == 0 && stride % 8 == 0 && aligned16(x) && aligned16(wq) &&
+      (!wk || aligned16(wk)) && (!k_cache || (aligned16(k_cache) && aligned16(v_cache)))) {
+    const int parts = (int)grid.y;
+    const int64_t units = (int64_t)num_tokens * parts;
+    B200_DISPATCH_3(dtype, T, launch_pdl(rownorm_cache_vec_kernel<T>, dim3((unsigned)((units + 7) / 8)), dim3(256), 0,
+                                         (cudaStream_t)stream, (T*)x, stride, wq, wk, eps, (T*)k_cache, (T*)v_cache,
+                                         slots, slot_pairs, block_size, num_tokens, parts, nq, nk, nv));
+    return finish_launch();
+  }
   B200_DISPATCH_3(dtype, T, launch_pdl(rownorm_cache_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, (T*)x,
                                        stride, wq, wk, eps, (T*)k_cache, (T*)v_cache, slots, slot_pairs, block_size,
                                        nq, nk, nv));

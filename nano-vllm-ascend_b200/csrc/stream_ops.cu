@@ -432,15 +432,16 @@ masked_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int64_t ro
 // (ctx_lens; C == 1; the columns are the last nk positions). HM >= H bounds the per-thread column of heads.
 template <typename T, int HM>
 __global__ void __launch_bounds__(256)
-mixed_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int C, int G, int rep, int nk, float scale,
+mixed_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int C, int G, int rep, int nk, int ns, float scale,
                      int window, const float* __restrict__ slopes, const float* __restrict__ talk,
                      const float* __restrict__ sink, const int* __restrict__ ctx_lens,
                      const int* __restrict__ chunk_first, const int* __restrict__ chunk_lo) {
-  extern __shared__ float sm[];                       // [H][nk] then talk [H][H]
+  extern __shared__ __align__(16) float smem_all[];   // talk [H][HM] (columns past H are zero), then x [H][ns]
   pdl_wait();
   const int H = G * rep;
   const int b = blockIdx.y, c = blockIdx.x;
-  float* stalk = sm + (size_t)H * nk;
+  float* stalk = smem_all;
+  float* sm = smem_all + (size_t)H * HM;              // ns >= the most keys any token sees (the window, or nk)
   int pos, key_lo;
   if (chunk_first != nullptr) {
     pos = chunk_first[b] + c;
@@ -454,34 +455,49 @@ mixed_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int C, int 
   if (window > 0) lo = max(lo, pos - window + 1 - key_lo);
   const int nv = max(0, hi - lo);
   if (talk != nullptr)
-    for (int e = threadIdx.x; e < H * H; e += blockDim.x) stalk[e] = talk[e];
-  auto row_of = [&](int h) { return (((int64_t)b * G + h / rep) * C + c) * rep + h % rep; };
-  for (int h = 0; h < H; ++h) {
-    const float* sr = s + row_of(h) * nk;
-    const float slope = slopes != nullptr ? slopes[h] : 0.f;
-    for (int j = threadIdx.x; j < nv; j += blockDim.x)
-      sm[(size_t)h * nk + j] = sr[lo + j] * scale - slope * (float)(pos - (key_lo + lo + j));
+    for (int e = threadIdx.x; e < H * HM; e += blockDim.x) stalk[e] = e % HM < H ? talk[(e / HM) * H + e % HM] : 0.f;
+  const int64_t row0 = ((int64_t)b * G * C + c) * rep;                       // row of head (g, r): row0 + g C rep + r
+  const int64_t gstep = (int64_t)C * rep;
+  // every thread keeps several loads in flight: one pass over (head, key) pairs, four heads per step
+  for (int h0 = 0; h0 < H; h0 += 4) {
+    for (int j = threadIdx.x; j < nv; j += blockDim.x) {
+      float raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int h = h0 + u;
+        raw[u] = h < H ? s[(row0 + (h / rep) * gstep + h % rep) * nk + lo + j] : 0.f;
+      }
+      const float dist = (float)(pos - (key_lo + lo + j));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int h = h0 + u;
+        if (h < H) sm[(size_t)h * ns + j] = raw[u] * scale - (slopes != nullptr ? slopes[h] : 0.f) * dist;
+      }
+    }
   }
   __syncthreads();
   if (talk != nullptr) {
     for (int j = threadIdx.x; j < nv; j += blockDim.x) {                     // a thread mixes one key's column of heads
       float v[HM];
 #pragma unroll
-      for (int g = 0; g < HM; ++g) v[g] = g < H ? sm[(size_t)g * nk + j] : 0.f;
+      for (int g = 0; g < HM; ++g) v[g] = g < H ? sm[(size_t)g * ns + j] : 0.f;
       for (int h = 0; h < H; ++h) {
-        const float* tr = stalk + h * H;
-        float d = 0.f;
+        const float4* tr = reinterpret_cast<const float4*>(stalk + h * HM);     // one broadcast load per four heads
+        float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-        for (int g = 0; g < HM; ++g)
-          if (g < H) d += tr[g] * v[g];
-        sm[(size_t)h * nk + j] = d;
+        for (int g = 0; g < HM / 4; ++g) {
+          const float4 t4 = tr[g];
+          d0 += t4.x * v[4 * g] + t4.z * v[4 * g + 2];
+          d1 += t4.y * v[4 * g + 1] + t4.w * v[4 * g + 3];
+        }
+        sm[(size_t)h * ns + j] = d0 + d1;
       }
     }
     __syncthreads();
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int h = warp; h < H; h += nw) {
-    float* x = sm + (size_t)h * nk;
+    float* x = sm + (size_t)h * ns;
     float m = -INFINITY;
     for (int j = lane; j < nv; j += 32) m = fmaxf(m, x[j]);
     m = warp_max(m);
@@ -495,7 +511,7 @@ mixed_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int C, int 
     }
     l = warp_sum(l) + (sink != nullptr ? expf(sk - m) : 0.f);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    T* pr = p + row_of(h) * nk;
+    T* pr = p + (row0 + (h / rep) * gstep + h % rep) * nk;
     for (int j = lane; j < nk; j += 32) pr[j] = from_f32<T>((j >= lo && j < hi) ? x[j - lo] * inv : 0.f);
   }
 }
@@ -517,7 +533,9 @@ extern "C" int b200_mixed_softmax(void* p, const float* s, int32_t entries, int3
   B200_RETURN_IF(ctx_lens && tokens_per_entry != 1, B200_ERR_BAD_SHAPE);
   const int H = num_kv_heads * rep;
   B200_RETURN_IF(H > 64 || entries > 65535, B200_ERR_UNSUPPORTED);
-  const size_t smem = ((size_t)H * nk + (size_t)H * H) * sizeof(float);
+  const int hm = H <= 4 ? 4 : H <= 8 ? 8 : H <= 16 ? 16 : H <= 32 ? 32 : 64;
+  const int ns = window > 0 && window < nk ? window : nk;          // no token sees more keys than its window holds
+  const size_t smem = ((size_t)H * ns + (size_t)H * hm) * sizeof(float);
   B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
   const dim3 grid(tokens_per_entry, entries);
 #define B200_MIXSM(HMV)                                                                                              \
@@ -525,8 +543,8 @@ extern "C" int b200_mixed_softmax(void* p, const float* s, int32_t entries, int3
     if (smem > 48 * 1024)                                                                                            \
       cudaFuncSetAttribute(mixed_softmax_kernel<T, HMV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     launch_pdl(mixed_softmax_kernel<T, HMV>, grid, dim3(256), smem, (cudaStream_t)stream, (T*)p, s,                  \
-               tokens_per_entry, num_kv_heads, rep, nk, scale, window, slopes, talk, sink, ctx_lens, chunk_first,    \
-               chunk_lo);                                                                                            \
+               tokens_per_entry, num_kv_heads, rep, nk, ns, scale, window, slopes, talk, sink, ctx_lens,             \
+               chunk_first, chunk_lo);                                                                               \
   })
   if (H <= 4) B200_MIXSM(4);
   else if (H <= 8) B200_MIXSM(8);

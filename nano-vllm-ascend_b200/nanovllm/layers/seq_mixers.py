@@ -240,9 +240,10 @@ class MixedHeadAttention(nn.Module):
         return dict(window=self.window, slopes=self.slopes, talk=self.talk, sink=self.sink)
 
     def _fits(self, nk: int) -> bool:
-        """The softmax kernel keeps a token's heads x keys block (and the mixing matrix) in shared memory."""
+        """The softmax kernel keeps a token's heads x visible keys block (and the mixing matrix) in shared memory."""
         H = self.num_heads
-        return (H * nk + H * H) * 4 <= ops.MIXED_SOFTMAX_SMEM
+        ns = min(nk, self.window) if self.window else nk
+        return (H * ns + H * max(4, 1 << (H - 1).bit_length())) * 4 <= ops.MIXED_SOFTMAX_SMEM
 
     DECODE_WINDOW_MAX = 4096      # decode steps gather a window of at most this many rows per sequence
     PRODUCT_BYTES = 512 << 20     # fp32 scores held at a time
