@@ -260,15 +260,19 @@ class MixedHeadAttention(nn.Module):
         G, dv, bs = self.num_kv_heads, self.vdim, ctx.block_size
         rep = H // G
         W = min(self.window, ctx.block_tables.shape[1] * bs)                 # no sequence holds more rows than its table
-        slots = ctx.scratch.get(("window rows", W))                          # the same for every layer of the step
-        if slots is None:
+        key = ("window rows by kv head", W, G)                               # the same for every layer of the step
+        idx = ctx.scratch.get(key)
+        if idx is None:
             pos = ctx.context_lens.long() - 1                                # -1 on padded rows
             j = (pos[:, None] - (W - 1) + torch.arange(W, device=q.device)).clamp(min=0)
             blocks = ctx.block_tables.gather(1, j // bs).clamp(min=0).long()
-            slots = ctx.scratch[("window rows", W)] = (blocks * bs + j % bs).view(-1)
-        krows = self.k_cache.view(-1, G * d)[slots].view(B, W, G, d).permute(0, 2, 3, 1).reshape(B * G, d, W)
-        vrows = self.v_cache.view(-1, G * dv)[slots].view(B, W, G, dv).permute(0, 2, 1, 3).reshape(B * G, W, dv)
-        scores = torch.bmm(q.reshape(B * G, rep, d), krows, out_dtype=torch.float32)          # [B * G, rep, W]
+            slots = blocks * bs + j % bs                                     # [B, W]
+            idx = ctx.scratch[key] = (slots[:, None, :].expand(B, G, W).contiguous(),
+                                      torch.arange(G, device=q.device)[None, :, None].expand(B, G, W).contiguous())
+        # ONE gather per cache, straight into [B, G, W, size]: the batched products want a kv head's rows together
+        krows = self.k_cache.view(-1, G, d)[idx].view(B * G, W, d)
+        vrows = self.v_cache.view(-1, G, dv)[idx].view(B * G, W, dv)
+        scores = torch.bmm(q.reshape(B * G, rep, d), krows.transpose(1, 2), out_dtype=torch.float32)   # [B * G, rep, W]
         p = ops.mixed_softmax(scores.view(B, G, 1, rep, W), self.scale, self.window, q.dtype, self.slopes, self.talk,
                               self.sink, ctx_lens=ctx.context_lens)
         return torch.bmm(p.view(B * G, rep, W), vrows).reshape(B, H * dv)
@@ -303,19 +307,23 @@ class MixedHeadAttention(nn.Module):
         if NC == 0:
             return out
         NK = plan["NK"]
-        flat_k = self.k_cache.view(-1, G * d) if paged else k.reshape(T, G * d)
-        flat_v = self.v_cache.view(-1, G * dv) if paged else v.reshape(T, G * dv)
+        flat_k = self.k_cache.view(-1, G, d) if paged else k
+        flat_v = self.v_cache.view(-1, G, dv) if paged else v
+        by_head = ("kv heads", G)
+        if by_head not in plan:                      # the key ranges once more, by kv head: [chunks, G, NK] (+ head index)
+            ks = plan["kslots"].view(NC, 1, NK).expand(NC, G, NK).contiguous()
+            plan[by_head] = (ks, torch.arange(G, device=q.device)[None, :, None].expand(NC, G, NK).contiguous())
         per = max(1, min(256, self.PRODUCT_BYTES // (CH * H * NK * 4)))      # chunks per launch: bounded score memory
         for g0 in range(0, NC, per):
             g1 = min(NC, g0 + per)
             n = g1 - g0
-            kslots = plan["kslots"][g0 * NK:g1 * NK]
-            kt = flat_k[kslots].view(n, NK, G, d).permute(0, 2, 3, 1).reshape(n * G, d, NK)
-            vv = flat_v[kslots].view(n, NK, G, dv).permute(0, 2, 1, 3).reshape(n * G, NK, dv)
+            idx = (plan[by_head][0][g0:g1], plan[by_head][1][g0:g1])
+            kk = flat_k[idx].view(n * G, NK, d)          # ONE gather per tensor, straight into [chunks, G, NK, size]
+            vv = flat_v[idx].view(n * G, NK, dv)
             run = plan["run"]
             qs = q[run + g0 * CH:run + g1 * CH] if run is not None else q[plan["qrows"][g0 * CH:g1 * CH]]
             qs = qs.reshape(n, CH, G, rep, d).permute(0, 2, 1, 3, 4).reshape(n * G, CH * rep, d)
-            scores = torch.bmm(qs, kt, out_dtype=torch.float32)                                 # [n * G, CH * rep, NK]
+            scores = torch.bmm(qs, kk.transpose(1, 2), out_dtype=torch.float32)                 # [n * G, CH * rep, NK]
             p = ops.mixed_softmax(scores.view(n, G, CH, rep, NK), self.scale, self.window, q.dtype, self.slopes,
                                   self.talk, self.sink, chunks=(plan["first"][g0:g1], plan["lo"][g0:g1]))
             o = torch.bmm(p.view(n * G, CH * rep, NK), vv)                                      # [n * G, CH * rep, dv]

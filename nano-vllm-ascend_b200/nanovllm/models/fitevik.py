@@ -65,7 +65,8 @@ class Hgrn2Mixer(nn.Module):
 
     def __init__(self, width: int, m: dict, eps: float):
         super().__init__()
-        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        H, d = m["heads"], m["dim"]
+        dv = m.get("vdim", d)
         self.H, self.d, self.dv = H, d, dv
         self.sizes = [H * d, H * d, H * dv]                             # q | forget | v
         self.proj = MergedColumnParallelLinear(width, self.sizes)
@@ -85,7 +86,8 @@ class TalkingAttentionMixer(nn.Module):
 
     def __init__(self, width: int, m: dict, eps: float, lender: "TalkingAttentionMixer | None" = None):
         super().__init__()
-        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        H, d = m["heads"], m["dim"]
+        G, dv = m.get("kv_heads", H), m.get("vdim", d)         # absent: one kv head per query head, values as wide as keys
         self.H, self.G, self.d, self.dv, self.eps = H, G, d, dv, eps
         self.borrows = lender is not None
         self.sizes = [H * d, 0, 0] if self.borrows else [H * d, G * d, G * dv]           # q | k | v
@@ -93,7 +95,8 @@ class TalkingAttentionMixer(nn.Module):
         self.q_norm = small_param(H * d, fill=1.0)
         if not self.borrows:
             self.k_norm = small_param(G * d, fill=1.0)
-        self.attn = MixedHeadAttention(H, G, d, dv, float(m["scale"]), window=(m.get("mask") or {}).get("size", 0),
+        self.attn = MixedHeadAttention(H, G, d, dv, float(m.get("scale", d ** -0.5)),
+                                       window=int((m.get("mask") or {}).get("size", 0) or 0),
                                        slope_base=SLOPE_BASE, kv_source=lender.attn if lender is not None else None)
         self.o_proj = RowParallelLinear(H * dv, width)
 
