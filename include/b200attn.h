@@ -485,6 +485,13 @@ int b200_gate_prep(float* q_out, float* f_out, const void* q, int64_t q_stride, 
                    const float* bias, const float* lower, int32_t num_tokens, int32_t n, int32_t dtype,
                    b200_stream_t stream);
 
+/* out [entries, G, nk, head] = src rows picked by slot and regrouped per kv head: out[n][g][j] = head g of row
+ * slots[n * nk + j] of src (rows of G heads, row stride src_stride_bytes). 16-byte copies: head_bytes and the stride are
+ * multiples of 16. */
+int b200_gather_rows_by_head(void* out, const void* src, int64_t src_stride_bytes, const int64_t* slots,
+                             int64_t entries, int32_t nk, int32_t num_kv_heads, int32_t head_bytes,
+                             b200_stream_t stream);
+
 /* Softmax of heads that are mixed before it, over blocks of raw fp32 dot products s [entries, G, C, rep, nk] (entry:
  * a chunk of a prompt or a sequence of a decode step; C tokens per entry; head g * rep + r; nk key columns): x_h =
  * scale s_h - slopes[h] (pos - key); x'_h = sum_g talk[h, g] x_g; p = exp(x') / (sum over visible keys + exp(sink[h])),

@@ -13,6 +13,8 @@
 //   rownorm_cache        RMS norm of q and of k over the WHOLE projection (all heads at once), K/V scatter
 //   gate_prep            what a gated linear recurrence with tied input reads: silu(q) and the lower-bounded forget
 //                        gate l + (1 - l) sigmoid(f + bias), both fp32
+//   gather_rows_by_head  cache (or packed) rows picked by slot, written per kv head: [entries, G, keys, size] -- the
+//                        operand layout of attention composed of batched products
 //
 // All are bound by HBM traffic; arithmetic is fp32 whatever the element type. Shapes are free: no
 // multiple-of-8 rule, so that small and odd models run (a 16-byte path is taken where rows allow it).
@@ -822,6 +824,25 @@ gate_prep_kernel(float* __restrict__ q_out, float* __restrict__ f_out, const T* 
   }
 }
 
+// ------------------------------------------------------------------ rows by slot, regrouped per kv head
+// out[n][g][j][:] = src[slots[n * nk + j]][g][:] in 16-byte vectors (vph per head): one pass, no index arithmetic on
+// the host, the layout that a batched product per kv head reads.
+__global__ void __launch_bounds__(256)
+gather_rows_by_head_kernel(uint4* __restrict__ out, const char* __restrict__ src, int64_t src_stride_bytes,
+                           const int64_t* __restrict__ slots, int64_t total, int nk, int G, int vph) {
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vph);
+    const int64_t r = i / vph;
+    const int j = (int)(r % nk);
+    const int64_t ng = r / nk;
+    const int g = (int)(ng % G);
+    const int64_t n = ng / G;
+    const int64_t slot = slots[n * nk + j];
+    out[i] = *reinterpret_cast<const uint4*>(src + slot * src_stride_bytes + ((int64_t)g * vph + v) * 16);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -1083,5 +1104,22 @@ extern "C" int b200_gate_prep(float* q_out, float* f_out, const void* q, int64_t
   B200_DISPATCH_3(dtype, T, launch_pdl(gate_prep_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, q_out,
                                        f_out, (const T*)q, q_stride, (const T*)f, f_stride, bias, lower,
                                        (int64_t)num_tokens, n));
+  return finish_launch();
+}
+
+extern "C" int b200_gather_rows_by_head(void* out, const void* src, int64_t src_stride_bytes, const int64_t* slots,
+                                        int64_t entries, int32_t nk, int32_t num_kv_heads, int32_t head_bytes,
+                                        b200_stream_t stream) {
+  B200_RETURN_IF(entries < 0 || nk <= 0 || num_kv_heads <= 0 || head_bytes <= 0, B200_ERR_BAD_SHAPE);
+  if (entries == 0) return B200_OK;
+  B200_RETURN_IF(!out || !src || !slots, B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(head_bytes % 16 != 0 || src_stride_bytes % 16 != 0 || !aligned16(out) || !aligned16(src),
+                 B200_ERR_MISALIGNED);
+  const int vph = head_bytes / 16;
+  const int64_t total = entries * nk * num_kv_heads * vph;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  launch_pdl(gather_rows_by_head_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (uint4*)out,
+             (const char*)src, src_stride_bytes, slots, total, nk, num_kv_heads, vph);
   return finish_launch();
 }

@@ -260,18 +260,15 @@ class MixedHeadAttention(nn.Module):
         G, dv, bs = self.num_kv_heads, self.vdim, ctx.block_size
         rep = H // G
         W = min(self.window, ctx.block_tables.shape[1] * bs)                 # no sequence holds more rows than its table
-        key = ("window rows by kv head", W, G)                               # the same for every layer of the step
-        idx = ctx.scratch.get(key)
-        if idx is None:
+        slots = ctx.scratch.get(("window rows", W))                          # the same for every layer of the step
+        if slots is None:
             pos = ctx.context_lens.long() - 1                                # -1 on padded rows
             j = (pos[:, None] - (W - 1) + torch.arange(W, device=q.device)).clamp(min=0)
             blocks = ctx.block_tables.gather(1, j // bs).clamp(min=0).long()
-            slots = blocks * bs + j % bs                                     # [B, W]
-            idx = ctx.scratch[key] = (slots[:, None, :].expand(B, G, W).contiguous(),
-                                      torch.arange(G, device=q.device)[None, :, None].expand(B, G, W).contiguous())
+            slots = ctx.scratch[("window rows", W)] = (blocks * bs + j % bs).view(-1)
         # ONE gather per cache, straight into [B, G, W, size]: the batched products want a kv head's rows together
-        krows = self.k_cache.view(-1, G, d)[idx].view(B * G, W, d)
-        vrows = self.v_cache.view(-1, G, dv)[idx].view(B * G, W, dv)
+        krows = ops.gather_rows_by_head(self.k_cache.view(-1, G, d), slots, B, W).view(B * G, W, d)
+        vrows = ops.gather_rows_by_head(self.v_cache.view(-1, G, dv), slots, B, W).view(B * G, W, dv)
         scores = torch.bmm(q.reshape(B * G, rep, d), krows.transpose(1, 2), out_dtype=torch.float32)   # [B * G, rep, W]
         p = ops.mixed_softmax(scores.view(B, G, 1, rep, W), self.scale, self.window, q.dtype, self.slopes, self.talk,
                               self.sink, ctx_lens=ctx.context_lens)
@@ -309,17 +306,13 @@ class MixedHeadAttention(nn.Module):
         NK = plan["NK"]
         flat_k = self.k_cache.view(-1, G, d) if paged else k
         flat_v = self.v_cache.view(-1, G, dv) if paged else v
-        by_head = ("kv heads", G)
-        if by_head not in plan:                      # the key ranges once more, by kv head: [chunks, G, NK] (+ head index)
-            ks = plan["kslots"].view(NC, 1, NK).expand(NC, G, NK).contiguous()
-            plan[by_head] = (ks, torch.arange(G, device=q.device)[None, :, None].expand(NC, G, NK).contiguous())
         per = max(1, min(256, self.PRODUCT_BYTES // (CH * H * NK * 4)))      # chunks per launch: bounded score memory
         for g0 in range(0, NC, per):
             g1 = min(NC, g0 + per)
             n = g1 - g0
-            idx = (plan[by_head][0][g0:g1], plan[by_head][1][g0:g1])
-            kk = flat_k[idx].view(n * G, NK, d)          # ONE gather per tensor, straight into [chunks, G, NK, size]
-            vv = flat_v[idx].view(n * G, NK, dv)
+            kslots = plan["kslots"][g0 * NK:g1 * NK]     # ONE gather per tensor, straight into [chunks, G, NK, size]
+            kk = ops.gather_rows_by_head(flat_k, kslots, n, NK).view(n * G, NK, d)
+            vv = ops.gather_rows_by_head(flat_v, kslots, n, NK).view(n * G, NK, dv)
             run = plan["run"]
             qs = q[run + g0 * CH:run + g1 * CH] if run is not None else q[plan["qrows"][g0 * CH:g1 * CH]]
             qs = qs.reshape(n, CH, G, rep, d).permute(0, 2, 1, 3, 4).reshape(n * G, CH * rep, d)

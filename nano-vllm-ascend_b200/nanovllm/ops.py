@@ -1125,6 +1125,25 @@ def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype, ctx_l
     return p
 
 
+def gather_rows_by_head(src, slots, entries, nk):
+    """src [rows, G, size] (a cache viewed per head, or a row-strided view of packed rows); slots int64 [entries * nk] ->
+    [entries, G, nk, size] with out[n, g, j] = src[slots[n * nk + j], g]: rows picked by slot and regrouped per kv head,
+    the operand layout of a batched product per head. 16-byte copies where head size and row stride allow them, else
+    torch indexing."""
+    _need_cuda(src, slots)
+    rows, G, size = src.shape
+    if slots.dtype != torch.int64 or not slots.is_contiguous() or slots.numel() != entries * nk:
+        raise TypeError("slots are contiguous int64 [entries * nk]")
+    item = src.element_size()
+    if (src.stride(2) != 1 or src.stride(1) != size or (size * item) % 16 or (src.stride(0) * item) % 16 or
+            src.data_ptr() % 16):
+        return src[slots].view(entries, nk, G, size).permute(0, 2, 1, 3).contiguous()
+    out = torch.empty(entries, G, nk, size, dtype=src.dtype, device=src.device)
+    _C.check(_C.load().b200_gather_rows_by_head(out.data_ptr(), src.data_ptr(), src.stride(0) * item, slots.data_ptr(),
+                                                entries, nk, G, size * item, _stream()), "b200_gather_rows_by_head")
+    return out
+
+
 MIXED_SOFTMAX_SMEM = 200 * 1024      # a token's heads x visible keys block (+ the mixing matrix) lives in shared memory
 
 

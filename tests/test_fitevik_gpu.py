@@ -733,3 +733,19 @@ def test_decode_rows_inside_a_window_on_library_products(window):
     assert float(got[6].abs().max()) == 0.0
     if window == 19:
         assert float(got[3, 1].mean()) > 2.0 > float(got[4, 1].mean())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rows_by_slot_regrouped_per_head(dtype):
+    """The gather that feeds the batched products: rows picked by slot (repeats, any order) land as [entries, G, keys,
+    size]; from a cache and from a row-strided view of packed rows; sizes that rule out 16-byte copies take the fallback."""
+    from nanovllm import ops
+    g = torch.Generator().manual_seed(7)
+    for G, size, extra in ((2, 24, 40), (4, 64, 0), (3, 5, 3)):
+        rows = 57
+        wide = torch.randn(rows, extra + G * size, generator=g).to(dtype).cuda()
+        src = wide[:, extra:].unflatten(1, (G, size))                       # a view whose rows are `extra` apart
+        slots = torch.randint(0, rows, (3 * 11,), generator=g).cuda()
+        got = ops.gather_rows_by_head(src, slots, 3, 11)
+        want = src[slots].view(3, 11, G, size).permute(0, 2, 1, 3)
+        assert got.shape == (3, G, 11, size) and torch.equal(got, want)

@@ -118,7 +118,7 @@ def test_random_init_is_finite_and_shares_the_head_norm():
     model.random_init(1)
     rec = model.layers[0].mix
     assert torch.equal(rec.norm.weight[:rec.dv], rec.norm.weight[rec.dv:2 * rec.dv])
-    assert float(rec.rec.lower.min()) >= 0.0 and float(rec.rec.lower.max()) < 1.0
+    assert float(rec.rec.lower.detach().min()) >= 0.0 and float(rec.rec.lower.detach().max()) < 1.0
     assert all(torch.isfinite(p).all() for p in model.parameters())
 
 
