@@ -523,12 +523,16 @@ int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t inter, int3
  * (block_tables == NULL: k, v are this step's rows in the order of cu_k) or paged caches
  * [nb, bs, G*dim] / [nb, bs, G*vdim]. q [T, H, dim] -> out [T, H*vdim]. fp32 scores and accumulation.
  * window > 0: the query at position i sees keys j with 0 <= i - j < window. v == NULL: the values are the
- * first vdim columns of the key rows (one cached latent row serves as key and as value; vdim <= dim). */
+ * first vdim columns of the key rows (one cached latent row serves as key and as value; vdim <= dim).
+ * softcap > 0: scores become softcap * tanh(score / softcap). sink (fp32 [H] or NULL): exp(sink[h]) joins the softmax
+ * denominator without a value. gate ([T, gate_stride] of dtype, or NULL): head h of token t is multiplied by
+ * sigmoid(gate[t, h]). */
 int b200_attn_generic(void* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
                       const void* v, int64_t v_stride, const int32_t* block_tables, int32_t bt_stride,
                       int32_t block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
                       int32_t num_seqs, int32_t max_q, int32_t num_heads, int32_t num_kv_heads, int32_t dim,
-                      int32_t vdim, float scale, int32_t window, int32_t dtype, b200_stream_t stream);
+                      int32_t vdim, float scale, int32_t window, float softcap, const float* sink, const void* gate,
+                      int64_t gate_stride, int32_t dtype, b200_stream_t stream);
 
 /* Per head S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t; S fp32 [kdim, vdim] in state
  * [slots, H, kdim, vdim]. q, k [T, groups*kdim] (head h reads group h / (H / groups)), v [T, H*vdim];
@@ -622,6 +626,13 @@ int b200_moe_route_grouped(int32_t* topk_ids, float* topk_weights, const float* 
                            int64_t logit_stride, const float* bias, int32_t tokens, int32_t num_experts,
                            int32_t top_k, int32_t groups, int32_t keep, float scale, b200_stream_t stream);
 
+/* Router: s = softmax(logits) over all experts (fp32 [T, E]); experts form `groups` equal groups of neighbours, a
+ * group scores its largest s and only the `keep` best groups stay in play; the top_k s are taken (ties to the lower
+ * index); weights = s / (sum s + 1e-20) * scale, fp32. */
+int b200_moe_route_grouped_softmax(int32_t* topk_ids, float* topk_weights, const float* router_logits,
+                                   int64_t logit_stride, int32_t tokens, int32_t num_experts, int32_t top_k,
+                                   int32_t groups, int32_t keep, float scale, b200_stream_t stream);
+
 /* The k largest of router_logits + bias (fp32 [tokens, E]); weights = softmax over the chosen logits only. */
 int b200_moe_route_topk(int32_t* topk_ids, float* topk_weights, const float* router_logits, int64_t logit_stride,
                         const float* bias, int32_t tokens, int32_t num_experts, int32_t top_k,
@@ -630,16 +641,45 @@ int b200_moe_route_topk(int32_t* topk_ids, float* topk_weights, const float* rou
 /* Expert GEMMs for any sizes and dtypes over the plan of b200_moe_align. gate_up == 1: out [pairs, n_out] (dtype) =
  * silu(x Wg^T) * (x Wu^T), x rows gathered by sorted_pair / top_k, w [E, 2*n_out, K]. gate_up == 2 + act: out
  * [pairs, n_out] (dtype) = act(x Wu^T) without a gate, w [E, n_out, K], act as in b200_act_only. gate_up == 0: out
- * [pairs, n_out] fp32 = a W^T with a [pairs, K] in plan order, w [E, n_out, K]. */
+ * [pairs, n_out] fp32 = a W^T with a [pairs, K] in plan order, w [E, n_out, K]. gate_up == 1 with glu_limit > 0: the
+ * clamped unit g sigmoid(glu_alpha g) (u + 1), g = min(x Wg^T, limit), u = clamp(x Wu^T, +-limit), in place of silu. */
 int b200_moe_gemm_generic(void* out, const void* a, int64_t a_stride, const void* w, const int32_t* offsets,
                           const int32_t* sorted_pair, int32_t num_pairs, int32_t K, int32_t n_out,
-                          int32_t num_local, int32_t top_k, int32_t gate_up, int32_t dtype,
-                          b200_stream_t stream);
+                          int32_t num_local, int32_t top_k, int32_t gate_up, float glu_alpha, float glu_limit,
+                          int32_t dtype, b200_stream_t stream);
 
 /* out[t] = sum_j topk_weights[t, j] y[pos_of_pair[t, j]] (fp32 accumulation, pairs with pos < 0 skipped). */
 int b200_moe_combine_weighted(void* out, const float* y, const float* topk_weights, const int32_t* pos_of_pair,
                               int32_t tokens, int32_t top_k, int32_t hidden, int32_t dtype,
                               b200_stream_t stream);
+
+/* residual (fp32 [rows, hidden], in place) <- (accumulate ? residual : 0) + c * scale[i] * y[r, i] (scale fp32
+ * [hidden] or NULL: c alone; y NULL: unchanged; y_index int64 [rows]: row r of y is y[clamp(y_index[r], 0, y_rows - 1)],
+ * a table lookup). Then, when weight is given: h (dtype) = residual / sqrt(mean over the element's group of
+ * residual^2 + eps) * (offset + weight), the row split into `groups` equal consecutive parts. */
+int b200_residual_scale_groupnorm(void* h, float* residual, const void* y, const int64_t* y_index, int64_t y_rows,
+                                  const float* scale, float c, int32_t accumulate, const float* weight, float offset,
+                                  float eps, int32_t rows, int32_t hidden, int32_t groups, int32_t dtype,
+                                  b200_stream_t stream);
+
+/* table [tokens, half, 2] fp32 = (cos, sin)(positions[t] * freq[i]) * magnitude; freq fp64 [half]; fp64 angles. */
+int b200_rotary_table(float* table, const int64_t* positions, const double* freq, double magnitude, int32_t tokens,
+                      int32_t half, b200_stream_t stream);
+
+/* In place on qkv [T, H*dim | G*dim | G*vdim] (row stride in elements): the first `dims` columns of every q and k
+ * head are rotated by table [T, dims/2, 2] in pairs (2i, 2i+1) (interleaved) or (i, i + dims/2); every value head
+ * becomes (1 - *lambda) v + *lambda v_other (v_other [T, G*vdim] with its row stride, or NULL: unchanged); k and v rows
+ * are stored at `slots` (flat, or (block, offset) pairs) of the paged caches [nb, bs, G*dim] / [nb, bs, G*vdim] when
+ * given. */
+int b200_rope_mix_cache(void* qkv, int64_t stride, const float* table, int32_t dims, int32_t interleaved,
+                        const void* v_other, int64_t v_other_stride, const float* lambda, void* k_cache, void* v_cache,
+                        const int32_t* slots, int32_t slot_pairs, int32_t block_size, int32_t num_tokens,
+                        int32_t num_heads, int32_t num_kv_heads, int32_t dim, int32_t vdim, int32_t dtype,
+                        b200_stream_t stream);
+
+/* out[t, h, :] = x[t, h, :] * sigmoid(gate[t * gate_stride + h]); x, out [rows, num_heads * vdim] contiguous. */
+int b200_head_gate(void* out, const void* x, const void* gate, int64_t gate_stride, int32_t rows, int32_t num_heads,
+                   int32_t vdim, int32_t dtype, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -6,8 +6,11 @@
 //                        group scores the sum of its two largest choices, only the `keep` best groups stay in
 //                        play (the others count as -inf); the top-k choices are taken and weighted by
 //                        s / (sum s + 1e-20) * scale. Ties go to the lower index. fp32 throughout.
+//   moe_route_grouped_softmax  s = softmax(z) over all experts; a group scores its largest s; the `keep` best groups
+//                        stay in play; the top-k s are taken and weighted by s / (sum s + 1e-20) * scale.
 //   moe_route_topk       the k largest of z + bias; weights = softmax over the chosen logits only. fp32 throughout.
-//   moe_gemm_generic     H[pos] = silu(X[token(pos)] Wg[e]^T) * (X[token(pos)] Wu[e]^T)   (gate_up)
+//   moe_gemm_generic     H[pos] = silu(X[token(pos)] Wg[e]^T) * (X[token(pos)] Wu[e]^T)   (gate_up; or the clamped unit
+//                        g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit))
 //                        H[pos] = act(X[token(pos)] Wu[e]^T)                               (up alone, no gate)
 //                        Y[pos] = H[pos] W2[e]^T, fp32                                     (down)
 //                        over the dispatch plan of moe_align (pairs sorted by expert); 32 x 64 tiles, fp32 FMA.
@@ -32,8 +35,19 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
   if (t >= tokens) return;
   float* choice = smem + (size_t)warp * 2 * E;
   float* sg = choice + E;
+  float zmax_all = -INFINITY, zsum_all = 0.f;
+  if (kind == 2) {                                   // softmax over ALL experts: the row's max and sum first
+    for (int e = lane; e < E; e += 32) zmax_all = fmaxf(zmax_all, logits[t * logit_stride + e]);
+    zmax_all = warp_max(zmax_all);
+    for (int e = lane; e < E; e += 32) zsum_all += expf(logits[t * logit_stride + e] - zmax_all);
+    zsum_all = warp_sum(zsum_all);
+  }
   for (int e = lane; e < E; e += 32) {
-    if (kind == 1) {                                 // the bias is part of the logit; weights: softmax over the chosen
+    if (kind == 2) {
+      const float s = expf(logits[t * logit_stride + e] - zmax_all) / zsum_all;
+      sg[e] = s;
+      choice[e] = s;
+    } else if (kind == 1) {                                 // the bias is part of the logit; weights: softmax over the chosen
       const float z = logits[t * logit_stride + e] + (bias != nullptr ? bias[e] : 0.f);
       sg[e] = z;
       choice[e] = z;
@@ -58,7 +72,7 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
           if (c > a) b = a, a = c;
           else if (c > b) b = c;
         }
-      gs[i] = g < groups ? (per > 1 ? a + b : a) : -INFINITY;
+      gs[i] = g < groups ? (per > 1 && kind != 2 ? a + b : a) : -INFINITY;   // kind 2: a group's largest score
     }
     unsigned kept[(kRouteMaxGroups + 31) / 32] = {0u, 0u};   // bit `lane` of word i: group lane + 32 i is kept
     for (int pick = 0; pick < keep; ++pick) {
@@ -130,6 +144,7 @@ struct MoeGenericParams {
   int64_t a_stride;
   int K, n_out, top_k;
   int act;                    // up alone: 0 silu, 1 relu, 2 gelu (tanh form), 3 squared relu
+  float glu_alpha, glu_limit; // gate_up with glu_limit > 0: g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up)
 };
 
 __device__ __forceinline__ float plain_act(float x, int act) {
@@ -211,7 +226,17 @@ moe_gemm_generic_kernel(const MoeGenericParams p) {
         const int c = n0 + tx * 4 + j;
         if (c >= p.n_out) continue;
         const int64_t o = (int64_t)(row_begin + r) * p.n_out + c;
-        if (kGateUp) reinterpret_cast<T*>(p.out)[o] = from_f32<T>(silu_f(acc[i][j]) * acc2[i][j]);
+        if (kGateUp) {
+          float r;
+          if (p.glu_limit > 0.f) {
+            const float g = fminf(acc[i][j], p.glu_limit);
+            const float u = fminf(fmaxf(acc2[i][j], -p.glu_limit), p.glu_limit);
+            r = g * sigmoid_f(p.glu_alpha * g) * (u + 1.0f);
+          } else {
+            r = silu_f(acc[i][j]) * acc2[i][j];
+          }
+          reinterpret_cast<T*>(p.out)[o] = from_f32<T>(r);
+        }
         else if (kMode == 2) reinterpret_cast<T*>(p.out)[o] = from_f32<T>(plain_act(acc[i][j], p.act));
         else reinterpret_cast<float*>(p.out)[o] = acc[i][j];
       }
@@ -256,6 +281,24 @@ extern "C" int b200_moe_route_grouped(int32_t* topk_ids, float* topk_weights, co
   return finish_launch();
 }
 
+extern "C" int b200_moe_route_grouped_softmax(int32_t* topk_ids, float* topk_weights, const float* router_logits,
+                                              int64_t logit_stride, int32_t tokens, int32_t num_experts,
+                                              int32_t top_k, int32_t groups, int32_t keep, float scale,
+                                              b200_stream_t stream) {
+  B200_RETURN_IF(tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts || groups <= 0 || keep <= 0 ||
+                     keep > groups || num_experts % groups != 0 || (num_experts / groups) * keep < top_k,
+                 B200_ERR_BAD_SHAPE);
+  B200_RETURN_IF(num_experts > kRouteMaxExperts || top_k > kRouteMaxTopK || groups > kRouteMaxGroups,
+                 B200_ERR_UNSUPPORTED);
+  if (tokens == 0) return B200_OK;
+  B200_RETURN_IF(!topk_ids || !topk_weights || !router_logits, B200_ERR_NULL_POINTER);
+  const size_t smem = (size_t)4 * 2 * num_experts * sizeof(float);
+  launch_pdl(moe_route_grouped_kernel, dim3((tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, topk_ids,
+             topk_weights, router_logits, logit_stride, (const float*)nullptr, tokens, num_experts, top_k, groups, keep,
+             scale, 2);
+  return finish_launch();
+}
+
 extern "C" int b200_moe_route_topk(int32_t* topk_ids, float* topk_weights, const float* router_logits,
                                    int64_t logit_stride, const float* bias, int32_t tokens, int32_t num_experts,
                                    int32_t top_k, b200_stream_t stream) {
@@ -272,13 +315,14 @@ extern "C" int b200_moe_route_topk(int32_t* topk_ids, float* topk_weights, const
 extern "C" int b200_moe_gemm_generic(void* out, const void* a, int64_t a_stride, const void* w,
                                      const int32_t* offsets, const int32_t* sorted_pair, int32_t num_pairs,
                                      int32_t K, int32_t n_out, int32_t num_local, int32_t top_k, int32_t gate_up,
-                                     int32_t dtype, b200_stream_t stream) {
+                                     float glu_alpha, float glu_limit, int32_t dtype, b200_stream_t stream) {
   B200_RETURN_IF(num_pairs < 0 || K <= 0 || n_out <= 0 || num_local <= 0 || top_k <= 0, B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(num_local > 65535, B200_ERR_UNSUPPORTED);
   if (num_pairs == 0) return B200_OK;
   B200_RETURN_IF(!out || !a || !w || !offsets || !sorted_pair, B200_ERR_NULL_POINTER);
   B200_RETURN_IF(gate_up < 0 || gate_up > 5, B200_ERR_BAD_SHAPE);
-  MoeGenericParams p{a, w, out, offsets, sorted_pair, a_stride, K, n_out, top_k, gate_up >= 2 ? gate_up - 2 : 0};
+  MoeGenericParams p{a, w, out, offsets, sorted_pair, a_stride, K, n_out, top_k, gate_up >= 2 ? gate_up - 2 : 0,
+                     glu_alpha, glu_limit};
   int my = (num_pairs + kGM - 1) / kGM;
   if (my > 32) my = 32;
   const dim3 grid((n_out + kGN - 1) / kGN, my, num_local);

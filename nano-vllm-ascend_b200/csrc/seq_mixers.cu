@@ -3,6 +3,8 @@
 //   attn_generic       causal softmax attention for ANY head sizes (key size != value size, sizes that are
 //                      not 64 or 128), any element type including fp32, packed or paged keys, and any mix of
 //                      prompt portions and single tokens in one launch. fp32 scores, softmax and accumulation.
+//                      Optional: a sliding window, scores capped by cap * tanh(s / cap), a sink logit per head that
+//                      joins the softmax denominator without a value, an output gate sigmoid(logit) per (token, head).
 //   linear_recurrence  S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t (+ d v_t) per head with the state S
 //                      [key size x value size] held in fp32 registers and carried between steps in a slot.
 //                      Three forms: a constant decay per head (lightning attention), a decay and a step size
@@ -27,7 +29,8 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
                     int64_t k_stride, const T* __restrict__ v, int64_t v_stride,
                     const int* __restrict__ block_tables, int bt_stride, int block_size,
                     const int* __restrict__ cu_q, const int* __restrict__ cu_k, const int* __restrict__ ctx_lens,
-                    int H, int G, int dim, int vdim, float scale, int window) {
+                    int H, int G, int dim, int vdim, float scale, int window, float softcap,
+                    const float* __restrict__ sink, const T* __restrict__ gate, int64_t gate_stride) {
   extern __shared__ float smem[];
   pdl_wait();
   const int s = blockIdx.z, g = blockIdx.y;
@@ -58,7 +61,8 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
   const int max_pos = sp.first_pos() + last_row / rep;
   const int64_t k_base = cu_k != nullptr && block_tables == nullptr ? cu_k[s] : 0;
 
-  float m = -INFINITY, l = 0.f, acc[kAttnMaxVChunks];
+  // a sink is one more entry of the softmax that has a logit and no value: the running state starts from it
+  float m = sink != nullptr ? sink[head] : -INFINITY, l = sink != nullptr ? 1.f : 0.f, acc[kAttnMaxVChunks];
 #pragma unroll
   for (int c = 0; c < kAttnMaxVChunks; ++c) acc[c] = 0.f;
 
@@ -92,6 +96,7 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
       const float* qr = sq + warp * dim;
       for (int i = 0; i < dim; ++i) d += qr[i] * kr[i];
       sc = d * scale;
+      if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
     }
     const float m_new = fmaxf(m, warp_max(sc));
     const float corr = expf(m - m_new);               // m = -inf on the first tile: exp(-inf) = 0
@@ -111,7 +116,8 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
   }
   if (!live) return;
   T* o = out + (int64_t)(sp.q_start + tok) * ((int64_t)H * vdim) + (int64_t)head * vdim;
-  const float inv = 1.0f / l;
+  float inv = 1.0f / l;
+  if (gate != nullptr) inv *= sigmoid_f(to_f32<T>(gate[(int64_t)(sp.q_start + tok) * gate_stride + head]));
 #pragma unroll
   for (int c = 0; c < kAttnMaxVChunks; ++c) {
     const int i = lane + 32 * c;
@@ -652,7 +658,8 @@ extern "C" int b200_attn_generic(void* out, const void* q, int64_t q_stride, con
                                  int32_t bt_stride, int32_t block_size, const int32_t* cu_q,
                                  const int32_t* cu_k, const int32_t* ctx_lens, int32_t num_seqs, int32_t max_q,
                                  int32_t num_heads, int32_t num_kv_heads, int32_t dim, int32_t vdim,
-                                 float scale, int32_t window, int32_t dtype, b200_stream_t stream) {
+                                 float scale, int32_t window, float softcap, const float* sink, const void* gate,
+                                 int64_t gate_stride, int32_t dtype, b200_stream_t stream) {
   B200_RETURN_IF(num_seqs < 0 || max_q < 0 || num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 ||
                      num_heads % num_kv_heads != 0, B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(vdim > 32 * kAttnMaxVChunks, B200_ERR_UNSUPPORTED);
@@ -671,7 +678,8 @@ extern "C" int b200_attn_generic(void* out, const void* q, int64_t q_stride, con
       cudaFuncSetAttribute(attn_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(attn_generic_kernel<T>, grid, dim3(kAttnRows * 32), smem, (cudaStream_t)stream, (T*)out,
                (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, block_tables, bt_stride,
-               block_size, cu_q, cu_k, ctx_lens, num_heads, num_kv_heads, dim, vdim, scale, window);
+               block_size, cu_q, cu_k, ctx_lens, num_heads, num_kv_heads, dim, vdim, scale, window, softcap, sink,
+               (const T*)gate, gate_stride);
   });
   return finish_launch();
 }

@@ -15,6 +15,12 @@
 //                        gate l + (1 - l) sigmoid(f + bias), both fp32
 //   gather_rows_by_head  cache (or packed) rows picked by slot, written per kv head: [entries, G, keys, size] -- the
 //                        operand layout of attention composed of batched products
+//   residual_scale_groupnorm  r (+)= c * scale[channel] * y (rows of y optionally gathered by index: the scaled token
+//                        embedding); h = RMS norm of r in equal consecutive groups, times a weight
+//   rotary_table         cos / sin of position * frequency for a table of frequencies (fp64 angles), times a magnitude
+//   rope_mix_cache       rotation of part of every q and k head by that table, values blended with another layer's
+//                        values of the same token, K/V scatter
+//   head_gate            every head of a row times sigmoid of one logit per (token, head)
 //
 // All are bound by HBM traffic; arithmetic is fp32 whatever the element type. Shapes are free: no
 // multiple-of-8 rule, so that small and odd models run (a 16-byte path is taken where rows allow it).
@@ -843,6 +849,211 @@ gather_rows_by_head_kernel(uint4* __restrict__ out, const char* __restrict__ src
   }
 }
 
+// ------------------------------------------------------------------ scaled residual add + grouped RMS norm
+// r <- (accumulate ? r : 0) + c * scale[i] * y[i]   (scale == nullptr: c alone; y == nullptr: r unchanged; y_index: row
+// t of y is y[clamp(y_index[t])], a table lookup);  h <- r / sqrt(mean over the element's group of r^2 + eps) *
+// (offset + w)   (skipped when w == nullptr). The row is split into `groups` equal consecutive parts.
+// Dynamic smem: hidden + groups floats. Group sums are taken by one warp per group in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_scale_groupnorm_kernel(T* __restrict__ h, float* __restrict__ res, const T* __restrict__ y,
+                                const int64_t* __restrict__ y_index, int64_t y_rows, const float* __restrict__ scale,
+                                float c, int accumulate, const float* __restrict__ w, float offset, float eps,
+                                int hidden, int groups) {
+  extern __shared__ float row[];                     // [hidden] then rstd [groups]
+  float* rstd = row + hidden;
+  pdl_wait();
+  float* r = res + (int64_t)blockIdx.x * hidden;
+  const T* yr = nullptr;
+  if (y != nullptr) {
+    int64_t src = blockIdx.x;
+    if (y_index != nullptr) src = min(max(y_index[blockIdx.x], (int64_t)0), y_rows - 1);
+    yr = y + src * hidden;
+  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = accumulate ? r[i] : 0.f;
+    if (yr != nullptr) {
+      const float u = c * (scale != nullptr ? scale[i] : 1.0f);
+      v += u * to_f32<T>(yr[i]);
+      r[i] = v;
+    }
+    row[i] = v;
+  }
+  if (w == nullptr) return;
+  __syncthreads();
+  const int per = hidden / groups;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < groups; g += nw) {
+    float ss = 0.f;
+    for (int i = lane; i < per; i += 32) ss += row[g * per + i] * row[g * per + i];
+    ss = warp_sum(ss);
+    if (lane == 0) rstd[g] = 1.0f / sqrtf(ss / (float)per + eps);
+  }
+  __syncthreads();
+  T* o = h + (int64_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(row[i] * rstd[i / per] * (offset + w[i]));
+}
+
+// 16-byte form (hidden % 8 == 0, group size % 8 == 0, hidden <= 8 * 256 * kResVecs): the row stays in registers; every
+// 8-element vector leaves its sum of squares in shared memory, one warp per group adds them in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_scale_groupnorm_vec_kernel(T* __restrict__ h, float* __restrict__ res, const T* __restrict__ y,
+                                    const int64_t* __restrict__ y_index, int64_t y_rows,
+                                    const float* __restrict__ scale, float c, int accumulate,
+                                    const float* __restrict__ w, float offset, float eps, int hidden, int groups) {
+  __shared__ float part[256 * kResVecs];
+  __shared__ float rstd[256];
+  pdl_wait();
+  const int nvec = hidden / 8;
+  float* r = res + (int64_t)blockIdx.x * hidden;
+  const T* yr = nullptr;
+  if (y != nullptr) {
+    int64_t src = blockIdx.x;
+    if (y_index != nullptr) src = min(max(y_index[blockIdx.x], (int64_t)0), y_rows - 1);
+    yr = y + src * hidden;
+  }
+  float val[kResVecs][8];
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      if (accumulate) {
+        load8<float>(r + vi * 8, val[n]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) val[n][e] = 0.f;
+      }
+      if (yr != nullptr) {
+        float yv[8], sv[8];
+        load8<T>(yr + vi * 8, yv);
+        if (scale != nullptr) {
+          load8<float>(scale + vi * 8, sv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) val[n][e] += (c * sv[e]) * yv[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) val[n][e] += c * yv[e];
+        }
+        store8<float>(r + vi * 8, val[n]);
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += val[n][e] * val[n][e];
+      part[vi] = ss;
+    }
+  }
+  if (w == nullptr) return;
+  __syncthreads();
+  const int vper = nvec / groups;                    // vectors per group
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < groups; g += nw) {
+    float ss = 0.f;
+    for (int i = lane; i < vper; i += 32) ss += part[g * vper + i];
+    ss = warp_sum(ss);
+    if (lane == 0) rstd[g] = 1.0f / sqrtf(ss / (float)(vper * 8) + eps);
+  }
+  __syncthreads();
+  T* o = h + (int64_t)blockIdx.x * hidden;
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      float wv[8], ov[8];
+      load8<float>(w + vi * 8, wv);
+      const float rs = rstd[vi / vper];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ov[e] = val[n][e] * rs * (offset + wv[e]);
+      store8<T>(o + vi * 8, ov);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ rotary positions from a table of frequencies
+// table[t][i] = (cos, sin)(positions[t] * freq[i]) * magnitude: fp64 angle (a position times a frequency loses digits
+// in fp32 at long range), fp32 result. Computed once per step for all layers that share the frequencies.
+__global__ void __launch_bounds__(256)
+rotary_table_kernel(float2* __restrict__ table, const int64_t* __restrict__ positions, const double* __restrict__ freq,
+                    double magnitude, int tokens, int half) {
+  pdl_wait();
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (int64_t)tokens * half) return;
+  const int t = (int)(e / half), i = (int)(e % half);
+  double sn, cs;
+  sincos((double)positions[t] * freq[i], &sn, &cs);
+  table[e] = make_float2((float)(cs * magnitude), (float)(sn * magnitude));
+}
+
+// qkv: [T, H*dim | G*dim | G*vdim] (row stride given), rewritten in place. Every q and k head: the first `dims`
+// columns are rotated by the table, in pairs (2i, 2i+1) (interleaved) or (i, i + dims/2); the rest pass. Every value
+// head: v <- (1 - lambda) v + lambda v_other (lambda a device scalar; skipped when v_other == nullptr). k and v rows are
+// also stored at their cache slot when caches are bound. One warp per (token, head of q | k | v); fp32 arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_mix_cache_kernel(T* __restrict__ qkv, int64_t stride, const float2* __restrict__ table, int dims, int interleaved,
+                      const T* __restrict__ v_other, int64_t v_other_stride, const float* __restrict__ lambda,
+                      T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots, int slot_pairs,
+                      int block_size, int num_tokens, int H, int G, int dim, int vdim) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int per_tok = H + 2 * G;
+  if (unit >= (int64_t)num_tokens * per_tok) return;
+  const int t = (int)(unit / per_tok), u = (int)(unit % per_tok);
+  int64_t slot = -1;
+  if (k_cache != nullptr && u >= H) {
+    slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+    if (slot < 0) k_cache = nullptr, v_cache = nullptr;      // a row without a cache slot is still rewritten in place
+  }
+  T* row = qkv + (int64_t)t * stride;
+  if (u >= H + G) {                                  // a value head
+    const int g = u - H - G;
+    T* x = row + (int64_t)(H + G) * dim + (int64_t)g * vdim;
+    T* dst = v_cache != nullptr ? v_cache + slot * ((int64_t)G * vdim) + (int64_t)g * vdim : nullptr;
+    if (v_other == nullptr) {
+      if (dst != nullptr)
+        for (int i = lane; i < vdim; i += 32) dst[i] = x[i];
+      return;
+    }
+    const float lam = *lambda;
+    const T* o = v_other + (int64_t)t * v_other_stride + (int64_t)g * vdim;
+    for (int i = lane; i < vdim; i += 32) {
+      const T v = from_f32<T>((1.0f - lam) * to_f32<T>(x[i]) + lam * to_f32<T>(o[i]));
+      x[i] = v;
+      if (dst != nullptr) dst[i] = v;
+    }
+    return;
+  }
+  T* x = row + (int64_t)u * dim;                     // q heads then k heads, both `dim` wide
+  T* dst = (u >= H && k_cache != nullptr) ? k_cache + slot * ((int64_t)G * dim) + (int64_t)(u - H) * dim : nullptr;
+  const int half = dims / 2;
+  const float2* cs = table + (int64_t)t * half;
+  for (int i = lane; i < half; i += 32) {
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    const float2 r = cs[i];
+    const float p = to_f32<T>(x[a]), q = to_f32<T>(x[b]);
+    const T ra = from_f32<T>(p * r.x - q * r.y), rb = from_f32<T>(q * r.x + p * r.y);
+    x[a] = ra, x[b] = rb;
+    if (dst != nullptr) dst[a] = ra, dst[b] = rb;
+  }
+  if (dst != nullptr)
+    for (int i = dims + lane; i < dim; i += 32) dst[i] = x[i];
+}
+
+// out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]): one logit per (token, head). In place when out == x.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ gate, int64_t gate_stride,
+                 int64_t total, int H, int vdim) {
+  pdl_wait();
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int64_t th = e / vdim;
+  const int64_t t = th / H;
+  const int hd = (int)(th % H);
+  out[e] = from_f32<T>(to_f32<T>(x[e]) * sigmoid_f(to_f32<T>(gate[t * gate_stride + hd])));
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -1121,5 +1332,78 @@ extern "C" int b200_gather_rows_by_head(void* out, const void* src, int64_t src_
   if (blocks > 148 * 32) blocks = 148 * 32;
   launch_pdl(gather_rows_by_head_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (uint4*)out,
              (const char*)src, src_stride_bytes, slots, total, nk, num_kv_heads, vph);
+  return finish_launch();
+}
+
+
+extern "C" int b200_residual_scale_groupnorm(void* h, float* residual, const void* y, const int64_t* y_index,
+                                             int64_t y_rows, const float* scale, float c, int32_t accumulate,
+                                             const float* weight, float offset, float eps, int32_t rows,
+                                             int32_t hidden, int32_t groups, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || hidden <= 0 || groups <= 0 || hidden % groups != 0 || (y_index && y_rows <= 0),
+                 B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!residual || (weight && !h) || (y_index && !y) || (!accumulate && !y), B200_ERR_NULL_POINTER);
+  const int per = hidden / groups;
+  if (hidden % 8 == 0 && per % 8 == 0 && hidden <= 8 * 256 * kResVecs && groups <= 256 && aligned16(residual) &&
+      (!y || aligned16(y)) && (!scale || aligned16(scale)) && (!weight || (aligned16(weight) && aligned16(h)))) {
+    const int threads = hidden / 8 >= 256 ? 256 : ((hidden / 8 + 31) / 32) * 32;
+    B200_DISPATCH_3(dtype, T, launch_pdl(residual_scale_groupnorm_vec_kernel<T>, dim3(rows), dim3(threads), 0,
+                                         (cudaStream_t)stream, (T*)h, residual, (const T*)y, y_index, y_rows, scale,
+                                         c, accumulate, weight, offset, eps, hidden, groups));
+    return finish_launch();
+  }
+  const size_t smem = (size_t)(hidden + groups) * sizeof(float);
+  B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
+  B200_DISPATCH_3(dtype, T, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(residual_scale_groupnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(residual_scale_groupnorm_kernel<T>, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (T*)h, residual,
+               (const T*)y, y_index, y_rows, scale, c, accumulate, weight, offset, eps, hidden, groups);
+  });
+  return finish_launch();
+}
+
+extern "C" int b200_rotary_table(float* table, const int64_t* positions, const double* freq, double magnitude,
+                                 int32_t tokens, int32_t half, b200_stream_t stream) {
+  B200_RETURN_IF(tokens < 0 || half <= 0, B200_ERR_BAD_SHAPE);
+  if (tokens == 0) return B200_OK;
+  B200_RETURN_IF(!table || !positions || !freq, B200_ERR_NULL_POINTER);
+  const int64_t total = (int64_t)tokens * half;
+  launch_pdl(rotary_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+             (float2*)table, positions, freq, magnitude, tokens, half);
+  return finish_launch();
+}
+
+extern "C" int b200_rope_mix_cache(void* qkv, int64_t stride, const float* table, int32_t dims, int32_t interleaved,
+                                   const void* v_other, int64_t v_other_stride, const float* lambda, void* k_cache,
+                                   void* v_cache, const int32_t* slots, int32_t slot_pairs, int32_t block_size,
+                                   int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dim,
+                                   int32_t vdim, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(num_tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 || dims < 0 ||
+                     dims > dim || dims % 2 != 0,
+                 B200_ERR_BAD_SHAPE);
+  if (num_tokens == 0) return B200_OK;
+  B200_RETURN_IF(!qkv || (dims > 0 && !table) || (k_cache == nullptr) != (v_cache == nullptr) || (k_cache && !slots) ||
+                     (v_other && !lambda),
+                 B200_ERR_NULL_POINTER);
+  const int64_t units = (int64_t)num_tokens * (num_heads + 2 * num_kv_heads);
+  const dim3 grid((unsigned)((units + 7) / 8));
+  B200_DISPATCH_3(dtype, T, launch_pdl(rope_mix_cache_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)qkv,
+                                       stride, (const float2*)table, dims, interleaved, (const T*)v_other,
+                                       v_other_stride, lambda, (T*)k_cache, (T*)v_cache, slots, slot_pairs, block_size,
+                                       num_tokens, num_heads, num_kv_heads, dim, vdim));
+  return finish_launch();
+}
+
+extern "C" int b200_head_gate(void* out, const void* x, const void* gate, int64_t gate_stride, int32_t rows,
+                              int32_t num_heads, int32_t vdim, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || num_heads <= 0 || vdim <= 0, B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!out || !x || !gate, B200_ERR_NULL_POINTER);
+  const int64_t total = (int64_t)rows * num_heads * vdim;
+  B200_DISPATCH_3(dtype, T, launch_pdl(head_gate_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                                       (cudaStream_t)stream, (T*)out, (const T*)x, (const T*)gate, gate_stride, total,
+                                       num_heads, vdim));
   return finish_launch();
 }

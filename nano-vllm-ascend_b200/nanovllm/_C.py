@@ -118,7 +118,8 @@ PROTOTYPES = {
     "b200_act_and_mul": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200_attn_generic": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                     c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
-                                    c_int32, c_int32, c_int32, c_float, c_int32, c_int32, c_void_p]),
+                                    c_int32, c_int32, c_int32, c_float, c_int32, c_float, c_void_p, c_void_p, c_int64,
+                                    c_int32, c_void_p]),
     "b200_linear_recurrence": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
@@ -163,7 +164,19 @@ PROTOTYPES = {
                                   c_int32, c_int32, c_int32, c_float, c_int32, c_void_p, c_void_p, c_void_p, c_int32,
                                   c_void_p]),
     "b200_moe_gemm_generic": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32,
-                                        c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+                                        c_int32, c_int32, c_int32, c_int32, c_int32, c_float, c_float, c_int32,
+                                        c_void_p]),
+    "b200_moe_route_grouped_softmax": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32,
+                                                 c_int32, c_int32, c_float, c_void_p]),
+    "b200_residual_scale_groupnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float,
+                                                c_int32, c_void_p, c_float, c_float, c_int32, c_int32, c_int32,
+                                                c_int32, c_void_p]),
+    "b200_rotary_table": (c_int32, [c_void_p, c_void_p, c_void_p, c_double, c_int32, c_int32, c_void_p]),
+    "b200_rope_mix_cache": (c_int32, [c_void_p, c_int64, c_void_p, c_int32, c_int32, c_void_p, c_int64, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                      c_int32, c_int32, c_int32, c_void_p]),
+    "b200_head_gate": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32,
+                                 c_void_p]),
     "b200_moe_combine_weighted": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                             c_int32, c_void_p]),
     "b200_sample": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_uint64,

@@ -120,6 +120,25 @@ def fitevik_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, h
             "max_positions": max_positions, "layers": layers}
 
 
+def nurilorn_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, head_dim: int = 128) -> dict:
+    """A Nurilorn configuration of realistic layer sizes for synthetic benchmarks: `pattern` is a string over
+    a (attention + dense feed-forward), e (attention + mixture of experts) and n (attention alone), repeated `repeats`
+    times. Every attention blends its values with the first layer's."""
+    H = width // head_dim
+    kv = max(1, H // 4)
+    mixer = {"heads": H, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "conv": 4, "scale": head_dim ** -0.5,
+             "softcap": 30.0, "v_mix": True,
+             "rot": {"dims": head_dim // 2, "base": 1e6,
+                     "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"a": {"kind": "dense", "ff": 3 * width, "limit": 7.0},
+           "e": {"kind": "moe", "expert": {"ff": width // 2, "limit": 7.0},
+                 "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}},
+           "n": None}
+    return {"architecture": "Nurilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "embedding": {"scale": float(width) ** 0.5}, "residual_mult": 0.5, "logit_scale": 0.25,
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": mlp[ch]} for ch in pattern] * repeats}
+
+
 def preset_hf_config(name: str):
     """Architecture presets built offline from the public model cards."""
     from transformers import LlamaConfig, Qwen3Config, Qwen3MoeConfig
@@ -140,6 +159,12 @@ def preset_hf_config(name: str):
         return NativeConfig(fitevik_preset(1024, "hgabhga", 4, vocab=151936))
     if key == "fitevik-2k":          # 16 layers at width 2048, head size 64: the size class of nirelix-2k
         return NativeConfig(fitevik_preset(2048, "hgab", 4, vocab=128256, head_dim=64))
+    if key == "nurilorn-1k":         # 28 layers at width 1024: the size class of zegopel-1k and qwen3-0.6b
+        return NativeConfig(nurilorn_preset(1024, "aeaeaea", 4, vocab=151936))
+    if key == "nurilorn-2k":         # 16 layers at width 2048, head size 64: the size class of zegopel-2k
+        return NativeConfig(nurilorn_preset(2048, "aeae", 4, vocab=128256, head_dim=64))
+    if key == "tiny-nurilorn":
+        return NativeConfig(nurilorn_preset(128, "aen", 1, vocab=512, head_dim=32))
     if key == "tiny-fitevik":
         return NativeConfig(fitevik_preset(128, "hgab", 1, vocab=512, head_dim=32, window=24, max_positions=512))
     if key == "qwen3-0.6b":

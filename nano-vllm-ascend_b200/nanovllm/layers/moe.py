@@ -140,6 +140,46 @@ class GroupedSigmoidMoe(nn.Module):
         return ops.moe_experts_generic(x, self.w13, self.w2, w, plan)
 
 
+class GroupedSoftmaxMoe(nn.Module):
+    """Mixture of experts with a softmax router: s = softmax(z) over all experts in fp32, experts form ``groups`` equal
+    groups of neighbours of which only the ``keep`` best (by their largest s) stay in play, ``top_k`` experts are chosen
+    and weighted by s / (sum of the chosen s + 1e-20). Experts are gate/up/down MLPs without biases, stacked in two
+    tensors; ``glu = (alpha, limit)`` selects the clamped unit g sigmoid(alpha g) (u + 1) with g = min(gate, limit),
+    u = clamp(up, +-limit) in place of silu(g) u. Prompt-sized batches of 16-bit models whose sizes fit run both products
+    on the grouped tcgen05 GEMM of csrc/moe_umma.cu with the unit between them; everything else (fp32, other sizes,
+    decode-sized batches) on the generic kernels of csrc/moe_generic.cu with fp32 routing weights."""
+
+    def __init__(self, hidden_size: int, inter: int, num_experts: int, top_k: int, groups: int = 1, keep: int = 1,
+                 glu: tuple[float, float] | None = None):
+        super().__init__()
+        if tp_rank_size()[1] != 1:
+            raise ValueError("GroupedSoftmaxMoe holds every expert on one GPU")
+        self.hidden_size, self.inter, self.num_experts, self.top_k = hidden_size, inter, num_experts, top_k
+        self.groups, self.keep, self.glu = groups, keep, glu
+        self.router = nn.Parameter(torch.empty(num_experts, hidden_size, dtype=torch.float32))
+        self.w13 = nn.Parameter(torch.empty(num_experts, 2 * inter, hidden_size))
+        self.w2 = nn.Parameter(torch.empty(num_experts, hidden_size, inter))
+        self.w13.weight_loader = self._load_w13
+        self.w2.weight_loader = lambda p, w, e: p.data[e].copy_(w)
+        self.fast = True           # False: always the generic kernels
+
+    def _load_w13(self, param, loaded, shard):
+        e, part = shard                                                  # part 0: gate rows, 1: up rows
+        param.data[e, part * self.inter:(part + 1) * self.inter].copy_(loaded)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        logits = F.linear(x.float(), self.router)
+        ids, w = ops.moe_route_grouped_softmax(logits, self.top_k, self.groups, self.keep)
+        plan = ops.moe_align(ids, 0, self.num_experts)
+        if (self.fast and x.dtype != torch.float32 and self.hidden_size % 128 == 0 and self.inter % 64 == 0
+                and self.top_k <= 8 and self.num_experts <= 256):
+            if self.glu is None:
+                return ops.moe_experts(x, self.w13, self.w2, ids, w.to(x.dtype), plan)
+            if x.shape[0] * self.top_k >= ops._MOE_BIG_GEMM_ROWS * self.num_experts:
+                return ops.moe_experts_glu_clamped(x, self.w13, self.w2, ids, w.to(x.dtype), plan, *self.glu)
+        return ops.moe_experts_generic(x, self.w13, self.w2, w, plan, glu=self.glu)
+
+
 class TopkSoftmaxMoe(nn.Module):
     """Mixture of experts whose router is a plain linear map with a bias, computed in fp32: the ``top_k`` experts with
     the largest logits are chosen and weighted by the softmax over the chosen logits only. Experts are feed-forwards

@@ -1,8 +1,9 @@
 """Building blocks of hybrid decoders: a short causal convolution with a carried tail, linear recurrences
 with an fp32 state (constant decay per head, the selective state-space form, a forget gate per key channel that also
 decides what is written, or the gated delta rule with a decay per key channel), the gated norms that follow them,
-rotary positions on part of a head, causal softmax attention whose key and value sizes may differ (optionally inside
-a sliding window), attention whose heads are mixed before the softmax (with a distance bias, a sink, and keys and
+rotary positions on part of a head (plain, or with frequencies stretched by a ramp between a fast and a slow band),
+causal softmax attention whose key and value sizes may differ (optionally inside a sliding window, with capped scores,
+a sink in the denominator and a gate per head), attention whose heads are mixed before the softmax (with a distance bias, a sink, and keys and
 values that may be another layer's), attention over a cached latent, and the mixing weights of a residual that is
 kept in several streams.
 
@@ -131,12 +132,20 @@ class VarSizeAttention(nn.Module):
     """Causal softmax attention with ``dim``-wide queries/keys and ``vdim``-wide values over paged caches
     ``k_cache`` [nb, bs, G*dim] / ``v_cache`` [nb, bs, G*vdim] (bound by the runner; K/V rows are written by the
     caller's fused epilogue). 16-bit models with dim == vdim in {64, 128} run on the tcgen05 prefill kernel and
-    the paged decode kernel of the dense decoders; everything else (other sizes, fp32) on the generic kernel."""
+    the paged decode kernel of the dense decoders; everything else (other sizes, fp32) on the generic kernel.
+    ``softcap`` c > 0 turns every score s into c tanh(s / c); ``sink`` (a logit) adds exp(sink) to every softmax
+    denominator, an entry without key or value; ``forward(..., gate)`` multiplies head h of token t by sigmoid(gate[t, h])."""
 
-    def __init__(self, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0):
+    def __init__(self, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0,
+                 softcap: float = 0.0, sink: float | None = None):
         super().__init__()
         self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.scale = num_heads, num_kv_heads, dim, vdim, scale
         self.window = int(window)                       # > 0: position i sees keys j with 0 <= i - j < window
+        self.softcap = float(softcap or 0.0)
+        if sink is not None:
+            self.register_buffer("sink", torch.full((num_heads,), float(sink), dtype=F32), persistent=False)
+        else:
+            self.sink = None
         self.k_cache = torch.tensor([])
         self.v_cache = torch.tensor([])
         self.layer_id = -1
@@ -147,29 +156,36 @@ class VarSizeAttention(nn.Module):
 
     def _fast(self, q) -> bool:
         rep, G = self.num_heads // self.num_kv_heads, self.num_kv_heads
-        return (not self.force_generic and not self.window and q.dtype in (torch.bfloat16, torch.float16) and self.dim == self.vdim
+        return (not self.force_generic and not self.window and not self.softcap and self.sink is None
+                and q.dtype in (torch.bfloat16, torch.float16) and self.dim == self.vdim
                 and self.dim in (64, 128) and rep <= 8 and (G in (1, 2, 4) or G % 8 == 0))
 
-    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-        """q [T, H, dim]; k [T, G, dim], v [T, G, vdim]: this step's rows (used when no cache is bound)."""
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+        """q [T, H, dim]; k [T, G, dim], v [T, G, vdim]: this step's rows (used when no cache is bound); gate [T, H]
+        logits of an output gate per head, or None."""
         ctx = get_context()
         paged = self.k_cache.numel() > 0 and ctx.block_tables is not None
         if self._fast(q) and (paged or ctx.is_prefill):
+            out = None
             if not ctx.is_prefill:
-                return ops.paged_decode_attn(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens,
-                                             self.scale, self.num_kv_heads, num_ctas=ctx.decode_attn_ctas)
-            if paged and ctx.block_size % 16 == 0:
-                return ops.prefill_varlen_attn(q, self.k_cache, self.v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
-                                               ctx.max_seqlen_q, ctx.max_seqlen_k, self.scale, self.num_kv_heads,
-                                               block_tables=ctx.block_tables)
-            if not paged:
-                return ops.prefill_varlen_attn(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                               ctx.max_seqlen_k, self.scale, self.num_kv_heads)
+                out = ops.paged_decode_attn(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens,
+                                            self.scale, self.num_kv_heads, num_ctas=ctx.decode_attn_ctas)
+            elif paged and ctx.block_size % 16 == 0:
+                out = ops.prefill_varlen_attn(q, self.k_cache, self.v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
+                                              ctx.max_seqlen_q, ctx.max_seqlen_k, self.scale, self.num_kv_heads,
+                                              block_tables=ctx.block_tables)
+            elif not paged:
+                out = ops.prefill_varlen_attn(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
+                                              ctx.max_seqlen_k, self.scale, self.num_kv_heads)
+            if out is not None:
+                out = out.view(q.shape[0], self.num_heads * self.vdim)
+                return out if gate is None else ops.head_gate_(out, gate, self.num_heads)
         spans = ops.StepSpans.of(ctx)
+        extras = dict(window=self.window, softcap=self.softcap, sink=self.sink, gate=gate)
         if paged:
             return ops.attn_generic(q, self.k_cache, self.v_cache, spans, self.scale, self.num_kv_heads, self.vdim,
-                                    block_tables=ctx.block_tables, window=self.window)
-        return ops.attn_generic(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, window=self.window)
+                                    block_tables=ctx.block_tables, **extras)
+        return ops.attn_generic(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, **extras)
 
 
 class MixedHeadAttention(nn.Module):
@@ -370,6 +386,48 @@ class Rotary:
         """x [T, heads, width] view -> rotated (and scaled) copy, see ops.rotary_heads."""
         return ops.rotary_heads(x, positions, x.shape[1], x.shape[2], self.dims, self.base, self.interleaved, out=out,
                                 out_f32=out_f32, split=split, scale_lo=scale_lo, scale_hi=scale_hi)
+
+
+class BandScaledRotary:
+    """Rotary positions whose frequencies are stretched band by band: f_i = base^(-2i/dims), i < dims/2; with
+    n(t) = dims ln(original / (2 pi t)) / (2 ln base) (the pair index that makes t turns over the original length),
+    lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+    the frequency becomes f_i / factor * ramp_i + f_i (1 - ramp_i): pairs that turn fast keep their frequency, slow
+    ones are divided by ``factor``, and cos and sin are multiplied by 0.1 ln(factor) + 1. Without ``scaling`` the
+    frequencies are the plain ones. The step's (cos, sin) table is computed once per pass (fp64 angles) and shared by
+    all layers with the same constants; the rotation itself runs fused with the layer's cache write
+    (ops.rope_mix_cache)."""
+
+    MAGNITUDE_SLOPE = 0.1
+
+    def __init__(self, dims: int, base: float, interleaved: bool = True, scaling: dict | None = None):
+        import math
+        self.dims, self.base, self.interleaved = int(dims), float(base), bool(interleaved)
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        self.magnitude = 1.0
+        if scaling:
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+            turns_at = lambda t: self.dims * math.log(original / (2 * math.pi * t)) / (2 * math.log(self.base))
+            lo = max(math.floor(turns_at(float(scaling["fast"]))), 0)
+            hi = min(math.ceil(turns_at(float(scaling["slow"]))), self.dims - 1)
+            ramp = [min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001))) for i in range(half)]
+            f = [fi / factor * r + fi * (1 - r) for fi, r in zip(f, ramp)]
+            self.magnitude = self.MAGNITUDE_SLOPE * math.log(factor) + 1.0
+        self.freq = torch.tensor(f, dtype=torch.float64)
+        self.key = ("rotary table", self.dims, self.interleaved, self.magnitude, tuple(f))
+
+    def table(self, positions: torch.Tensor) -> torch.Tensor | None:
+        """fp32 [T, dims/2, 2] for this pass's positions, from the context's per-pass scratch."""
+        if self.dims == 0:
+            return None
+        ctx = get_context()
+        t = ctx.scratch.get(self.key)
+        if t is None or t.shape[0] != positions.numel():
+            if self.freq.device != positions.device:
+                self.freq = self.freq.to(positions.device)
+            t = ctx.scratch[self.key] = ops.rotary_table(positions, self.freq, self.magnitude)
+        return t
 
 
 def prompt_chunk_plan(ctx, paged, device, chunk: int, window: int, min_tokens: int):

@@ -5,7 +5,9 @@ the reference's registry (models/models_map.py) also lists its MiniCPM and visio
 which this build deliberately leaves out. Zegopel (a hybrid of softmax attention, lightning attention and
 Mamba-2 layers) and Nirelix (retention, gated delta rule and latent attention on a residual kept in several
 streams) and Fitevik (HGRN2 recurrences and attention with mixed heads, a distance bias and a sink, on a residual
-with the norm on each sublayer's output) are additions; their config.json names them with an ``"architecture"`` string (config.NativeConfig). Qwen2 checkpoints are served by the Qwen3 class, as in the reference:
+with the norm on each sublayer's output) and Nurilorn (gated attention with capped scores, a sink, rotary positions
+stretched band by band and values blended across layers, on a residual with scaled branches and grouped norms) are
+additions; their config.json names them with an ``"architecture"`` string (config.NativeConfig). Qwen2 checkpoints are served by the Qwen3 class, as in the reference:
 the config's ``attention_bias`` decides between QKV bias (Qwen2) and QK-norm (Qwen3).
 """
 from __future__ import annotations
@@ -15,6 +17,7 @@ from .qwen3 import Qwen3ForCausalLM
 from .qwen3_moe import Qwen3MoeForCausalLM
 from .fitevik import FitevikForCausalLM
 from .nirelix import NirelixForCausalLM
+from .nurilorn import NurilornForCausalLM
 from .zegopel import ZegopelForCausalLM
 
 model_dict: dict[str, type] = {}
@@ -30,5 +33,6 @@ for _arch, _cls in (("Qwen3ForCausalLM", Qwen3ForCausalLM),
                     ("LlamaForCausalLM", LlamaForCausalLM),
                     ("Zegopel", ZegopelForCausalLM),
                     ("Nirelix", NirelixForCausalLM),
-                    ("Fitevik", FitevikForCausalLM)):
+                    ("Fitevik", FitevikForCausalLM),
+                    ("Nurilorn", NurilornForCausalLM)):
     register(_arch, _cls)

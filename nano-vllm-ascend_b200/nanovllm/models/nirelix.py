@@ -29,6 +29,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..layers.activation import ClampedGatedFeedForward
 from ..layers.embed_head import ParallelLMHead, VocabParallelEmbedding
 from ..layers.linear import MergedColumnParallelLinear, PaddedMergedLinear, ReplicatedLinear, RowParallelLinear, tp_rank_size
 from ..layers.moe import GroupedSigmoidMoe
@@ -140,26 +141,13 @@ class LatentAttentionMixer(nn.Module):
         return self.o_proj(self.gate(o, self.proj.part(p, 2)))
 
 
-class ClampedGatedFeedForward(nn.Module):
-    """W_down(g sigmoid(alpha g) (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit)."""
-
-    def __init__(self, width: int, ff: int, limit: float, alpha: float = GLU_ALPHA):
-        super().__init__()
-        self.limit, self.alpha = float(limit), float(alpha)
-        self.gate_up_proj = MergedColumnParallelLinear(width, [ff, ff])
-        self.down_proj = RowParallelLinear(ff, width)
-
-    def forward(self, h):
-        return self.down_proj(ops.glu_clamped(self.gate_up_proj(h), self.alpha, self.limit))
-
-
 MIXERS = {"retention": RetentionMixer, "channel_delta": ChannelDeltaMixer, "latent_attention": LatentAttentionMixer}
 
 
 def build_feed_forward(width: int, mlp: dict) -> nn.Module:
     kind = mlp.get("kind", "dense")
     if kind == "dense":
-        return ClampedGatedFeedForward(width, mlp["ff"], mlp["limit"])
+        return ClampedGatedFeedForward(width, mlp["ff"], mlp["limit"], GLU_ALPHA)
     if kind == "moe":
         r = mlp["router"]
         groups = r.get("groups") or {}

@@ -588,6 +588,41 @@ def moe_experts_ungated(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, top
     return _moe_combine(lib, y, topk_ids, plan, T, hidden, None, x)
 
 
+def moe_experts_glu_clamped(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_ids: torch.Tensor,
+                            topk_weights: torch.Tensor, plan: MoePlan, alpha: float, limit: float) -> torch.Tensor:
+    """Gated experts whose unit is the clamped one of glu_clamped, prompt-sized batches of 16-bit models on the grouped
+    tcgen05 GEMM: rows gathered by expert, gate and up rows of every expert as ONE product (w13 [E, 2*inter, hidden]),
+    the unit, the down product with the routing weights in its epilogue, the per-token combine. topk_weights [T, k] in
+    x's dtype. hidden % 128 == 0, inter % 64 == 0."""
+    _need_cuda(x, w13, w2, topk_ids, topk_weights)
+    T, hidden = x.shape
+    E, two_i, h2 = w13.shape
+    inter = two_i // 2
+    if h2 != hidden or w2.shape != (E, hidden, inter) or E != plan.num_local:
+        raise ValueError("expert weight shapes do not match")
+    if not (w13.is_contiguous() and w2.is_contiguous() and topk_weights.is_contiguous()):
+        raise ValueError("expert weights / routing weights must be contiguous")
+    if x.stride(1) != 1 or x.dtype != w13.dtype or x.dtype != w2.dtype or x.dtype != topk_weights.dtype:
+        raise ValueError("x must be row-major and share its dtype with the weights")
+    k = plan.top_k
+    pairs = T * k
+    lib = _C.load()
+    xs = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
+    gu = torch.empty(pairs, two_i, dtype=x.dtype, device=x.device)
+    y = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
+    _C.check(lib.b200_moe_gather_rows(xs.data_ptr(), x.data_ptr(), plan.offsets.data_ptr(), plan.sorted_pair.data_ptr(),
+                                      pairs, E, k, hidden, x.stride(0) if T > 1 else hidden, _dt(x), _stream()),
+             "b200_moe_gather_rows")
+    _C.check(lib.b200_moe_gemm_down_umma(gu.data_ptr(), xs.data_ptr(), w13.data_ptr(), plan.offsets.data_ptr(), None,
+                                         None, pairs, hidden, two_i, E, _dt(x), _stream()),
+             "b200_moe_gemm_down_umma (gate | up)")
+    h = glu_clamped(gu, alpha, limit)
+    _C.check(lib.b200_moe_gemm_down_umma(y.data_ptr(), h.data_ptr(), w2.data_ptr(), plan.offsets.data_ptr(),
+                                         plan.sorted_pair.data_ptr(), topk_weights.data_ptr(), pairs, inter, hidden, E,
+                                         _dt(x), _stream()), "b200_moe_gemm_down_umma")
+    return _moe_combine(lib, y, topk_ids, plan, T, hidden, None, x)
+
+
 def _moe_expert_gemms_library(x, w13, w2, topk_weights, plan: MoePlan) -> torch.Tensor:
     k = plan.top_k
     pair = plan.sorted_pair.long()                    # tail entries are 0: harmless rows, never combined
@@ -899,13 +934,21 @@ def mixed_attn(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_table
     return out
 
 
-def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tables=None, window=0):
+def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tables=None, window=0, softcap=0.0,
+                 sink=None, gate=None):
     """Causal softmax attention for any head sizes and dtypes. q [T, H, dim]; packed mode: k [Tk, G, dim],
     v [Tk, G, vdim] (token-strided views allowed) in the order of spans.cu_k; paged mode (block_tables given):
     k, v are the caches [nb, bs, G*dim], [nb, bs, G*vdim]. Returns [T, H*vdim]. window > 0: position i sees the
-    keys j with 0 <= i - j < window. v None: the values are the first vdim columns of the key rows."""
-    _need_cuda(q, k, v, block_tables)
+    keys j with 0 <= i - j < window. v None: the values are the first vdim columns of the key rows. softcap > 0:
+    scores become softcap * tanh(score / softcap). sink fp32 [H]: exp(sink[h]) joins the softmax denominator (no key,
+    no value). gate [T, H] (q's dtype, row-strided view allowed): head h of token t is multiplied by sigmoid(gate[t, h])."""
+    _need_cuda(q, k, v, block_tables, sink, gate)
+    _f32(sink)
     T, H, dim = q.shape
+    if sink is not None and sink.numel() != H:
+        raise ValueError("sink [H]")
+    if gate is not None and (gate.shape != (T, H) or gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise ValueError("gate [T, H] of q's dtype with unit inner stride")
     if q.stride(2) != 1 or q.stride(1) != dim:
         raise ValueError("q must be contiguous in (heads, dim)")
     G = num_kv_heads
@@ -929,7 +972,9 @@ def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tab
     _C.check(_C.load().b200_attn_generic(out.data_ptr(), q.data_ptr(), q.stride(0) if T > 1 else H * dim,
                                          k.data_ptr(), ks, _ptr(v), vs, bt_ptr, bt_stride, bs, cu_q, cu_k, ctx,
                                          spans.num_seqs, spans.max_q, H, G, dim, vdim, float(scale), int(window),
-                                         _dt3(q), _stream()), "b200_attn_generic")
+                                         float(softcap), _ptr(sink), _ptr(gate),
+                                         (gate.stride(0) if T > 1 else H) if gate is not None else 0, _dt3(q),
+                                         _stream()), "b200_attn_generic")
     return out
 
 
@@ -1203,6 +1248,23 @@ def moe_route_grouped(router_logits, bias, top_k, groups=1, keep=1, scale=1.0):
     return ids, w
 
 
+def moe_route_grouped_softmax(router_logits, top_k, groups=1, keep=1, scale=1.0):
+    """Softmax router with group-limited choice. router_logits fp32 [T, E]: s = softmax over all experts; a group of
+    neighbours scores its largest s, only the `keep` best of the `groups` groups stay in play; the top_k s are taken
+    (ties to the lower index) -> (topk_ids int32 [T, k], topk_weights fp32 [T, k] = s / (sum s + 1e-20) * scale)."""
+    _need_cuda(router_logits)
+    if router_logits.dtype != torch.float32 or router_logits.stride(1) != 1:
+        raise TypeError("router logits are fp32 with unit inner stride")
+    T, E = router_logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=router_logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=router_logits.device)
+    _C.check(_C.load().b200_moe_route_grouped_softmax(ids.data_ptr(), w.data_ptr(), router_logits.data_ptr(),
+                                                      router_logits.stride(0) if T > 1 else E, T, E, int(top_k),
+                                                      int(groups), int(keep), float(scale), _stream()),
+             "b200_moe_route_grouped_softmax")
+    return ids, w
+
+
 def moe_route_topk(router_logits, bias, top_k):
     """The top_k largest of router_logits + bias (fp32 [T, E]; bias fp32 [E] or None), weighted by the softmax over
     the chosen logits only -> (topk_ids int32 [T, k], topk_weights fp32 [T, k]). Ties go to the lower index."""
@@ -1219,9 +1281,10 @@ def moe_route_topk(router_logits, bias, top_k):
     return ids, w
 
 
-def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan, act=None) -> torch.Tensor:
+def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan, act=None, glu=None) -> torch.Tensor:
     """Expert MLPs and the weighted combine for any sizes and dtypes (fp32 included): x [T, hidden]; w2 [E, hidden,
-    inter]; topk_weights fp32 [T, k]. act None: gated experts down(silu(gate x) * up x) with w13 [E, 2*inter, hidden];
+    inter]; topk_weights fp32 [T, k]. act None: gated experts down(silu(gate x) * up x) with w13 [E, 2*inter, hidden]
+    (glu = (alpha, limit): the clamped unit g sigmoid(alpha g) (u + 1) of glu_clamped in place of silu(g) u);
     act "silu" | "relu" | "gelu_tanh" | "relu2": experts without a gate, down(act(up x)) with w13 [E, inter, hidden]."""
     _need_cuda(x, w13, w2, topk_weights)
     _f32(topk_weights)
@@ -1239,12 +1302,100 @@ def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan, act=None) -> to
     out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
     _C.check(lib.b200_moe_gemm_generic(h.data_ptr(), x.data_ptr(), x.stride(0) if T > 1 else hidden, w13.data_ptr(),
                                        plan.offsets.data_ptr(), plan.sorted_pair.data_ptr(), pairs, hidden, inter, E,
-                                       k, 1 if act is None else 2 + _PLAIN_ACTS[act], _dt3(x), _stream()),
+                                       k, 1 if act is None else 2 + _PLAIN_ACTS[act], float(glu[0]) if glu else 0.0,
+                                       float(glu[1]) if glu else 0.0, _dt3(x), _stream()),
              "b200_moe_gemm_generic (up)")
     _C.check(lib.b200_moe_gemm_generic(y.data_ptr(), h.data_ptr(), inter, w2.data_ptr(), plan.offsets.data_ptr(),
-                                       plan.sorted_pair.data_ptr(), pairs, inter, hidden, E, k, 0, _dt3(x),
+                                       plan.sorted_pair.data_ptr(), pairs, inter, hidden, E, k, 0, 0.0, 0.0, _dt3(x),
                                        _stream()), "b200_moe_gemm_generic (down)")
     _C.check(lib.b200_moe_combine_weighted(out.data_ptr(), y.data_ptr(), topk_weights.data_ptr(),
                                            plan.pos_of_pair.data_ptr(), T, k, hidden, _dt3(x), _stream()),
              "b200_moe_combine_weighted")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# Scaled residual with a grouped norm, rotary positions from a frequency table fused with value blending and the K/V
+# scatter, and the per-head output gate (csrc/seq_ops.cu).
+def residual_scale_groupnorm_(residual, y, scale, c, w, eps, groups, dtype, offset=0.0, accumulate=True, y_index=None):
+    """residual (fp32 [rows, hidden], in place) <- (residual if accumulate else 0) + c * scale * y, with scale fp32
+    [hidden] or None and y [rows, hidden] in `dtype` (or, with y_index int64 [rows], a table whose rows are looked up:
+    the scaled token embedding); y None leaves the residual as it is. Returns h = the residual's RMS norm over each of
+    `groups` equal consecutive parts times (offset + w) in `dtype`, or None when w is None."""
+    _need_cuda(residual, y, scale, w, y_index)
+    _f32(residual, scale, w)
+    rows, hidden = residual.shape
+    if y is not None:
+        if not y.is_contiguous() or y.shape[-1] != hidden or y.dtype != dtype or (y_index is None and y.shape[0] != rows):
+            raise ValueError("y: contiguous [rows or table, hidden] of the model dtype")
+        if y_index is not None and (y_index.dtype != torch.int64 or not y_index.is_contiguous() or y_index.numel() != rows):
+            raise TypeError("row indices are contiguous int64 [rows]")
+    if hidden % groups:
+        raise ValueError("the row does not split into equal groups")
+    h = torch.empty(rows, hidden, dtype=dtype, device=residual.device) if w is not None else None
+    _C.check(_C.load().b200_residual_scale_groupnorm(_ptr(h), residual.data_ptr(), _ptr(y), _ptr(y_index),
+                                                     y.shape[0] if y is not None else 0, _ptr(scale), float(c),
+                                                     1 if accumulate else 0, _ptr(w), float(offset), float(eps), rows,
+                                                     hidden, int(groups), _DT3[dtype], _stream()),
+             "b200_residual_scale_groupnorm")
+    return h
+
+
+def rotary_table(positions, freq, magnitude=1.0):
+    """positions int64 [T], freq fp64 [half] -> fp32 [T, half, 2] = (cos, sin)(position * freq) * magnitude, angles fp64."""
+    _need_cuda(positions, freq)
+    if positions.dtype != torch.int64 or not positions.is_contiguous():
+        raise TypeError("positions must be contiguous int64")
+    if freq.dtype != torch.float64 or not freq.is_contiguous():
+        raise TypeError("frequencies are a contiguous fp64 vector")
+    T, half = positions.numel(), freq.numel()
+    table = torch.empty(T, half, 2, dtype=torch.float32, device=positions.device)
+    _C.check(_C.load().b200_rotary_table(table.data_ptr(), positions.data_ptr(), freq.data_ptr(), float(magnitude), T,
+                                         half, _stream()), "b200_rotary_table")
+    return table
+
+
+def rope_mix_cache(qkv, table, num_heads, num_kv_heads, dim, vdim, dims, interleaved=True, v_other=None, lam=None,
+                   k_cache=None, v_cache=None, slots=None):
+    """In place on qkv [T, H*dim | G*dim | G*vdim]: the first `dims` columns of every q and k head are rotated by
+    table [T, dims/2, 2] (rotary_table) in pairs (2i, 2i+1) (interleaved) or (i, i + dims/2); with v_other [T, G*vdim]
+    (row-strided view allowed) and lam (fp32 scalar tensor) every value row becomes (1 - lam) v + lam v_other; k and v
+    rows are stored at `slots` of the paged caches [nb, bs, G*dim] / [nb, bs, G*vdim] when those are given."""
+    _need_cuda(qkv, table, v_other, lam, k_cache, v_cache, slots)
+    _f32(lam)
+    T = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] != num_heads * dim + num_kv_heads * (dim + vdim):
+        raise ValueError("qkv must be [T, H*dim + G*dim + G*vdim] with unit inner stride")
+    if dims and (table is None or table.dtype != torch.float32 or not table.is_contiguous() or
+                 table.shape != (T, dims // 2, 2)):
+        raise ValueError("table: contiguous fp32 [T, dims/2, 2]")
+    if v_other is not None and (v_other.shape != (T, num_kv_heads * vdim) or v_other.stride(1) != 1 or
+                                v_other.dtype != qkv.dtype or lam is None or lam.numel() != 1):
+        raise ValueError("v_other [T, G*vdim] of qkv's dtype with unit inner stride, and a scalar lam")
+    have = k_cache is not None and k_cache.numel() > 0
+    bs = 0
+    if have:
+        _, bs = _cache_dims(k_cache, num_kv_heads * dim)
+        _cache_dims(v_cache, num_kv_heads * vdim)
+        if slots.dtype != torch.int32 or not slots.is_contiguous():
+            raise TypeError("slots must be contiguous int32")
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise TypeError("caches must have the activations' dtype")
+    _C.check(_C.load().b200_rope_mix_cache(
+        qkv.data_ptr(), qkv.stride(0) if T > 1 else qkv.shape[1], _ptr(table), int(dims), 1 if interleaved else 0,
+        _ptr(v_other), (v_other.stride(0) if T > 1 else v_other.shape[1]) if v_other is not None else 0, _ptr(lam),
+        k_cache.data_ptr() if have else None, v_cache.data_ptr() if have else None, slots.data_ptr() if have else None,
+        1 if (have and slots.dim() == 2) else 0, bs, T, num_heads, num_kv_heads, dim, vdim, _dt3(qkv), _stream()),
+        "b200_rope_mix_cache")
+    return qkv
+
+
+def head_gate_(x, gate, num_heads):
+    """x [T, H*vdim] (contiguous, in place) times sigmoid(gate [T, H]) per head; gate may be a row-strided view."""
+    _need_cuda(x, gate)
+    T, n = x.shape
+    if not x.is_contiguous() or n % num_heads or gate.shape != (T, num_heads) or gate.stride(1) != 1 or gate.dtype != x.dtype:
+        raise ValueError("x contiguous [T, H*vdim]; gate [T, H] of x's dtype with unit inner stride")
+    _C.check(_C.load().b200_head_gate(x.data_ptr(), x.data_ptr(), gate.data_ptr(), gate.stride(0) if T > 1 else num_heads,
+                                      T, num_heads, n // num_heads, _dt3(x), _stream()), "b200_head_gate")
+    return x
