@@ -176,18 +176,6 @@ def test_whole_prompt_and_layers(tmp_path_factory, name, dtype):
     assert close(got, want, dtype, STRICT_BF16[name])
 
 
-def test_oracle_continues_a_sequence():
-    """The restatement itself: a prompt in one piece equals the same prompt continued from handed-over state."""
-    cfg = config_a()
-    tensors = O.random_weights(cfg, seed=3)
-    toks = tokens_of(cfg, 21, 8)
-    whole, _ = O.forward(cfg, tensors, toks)
-    a, st = O.forward(cfg, tensors, toks[:9])
-    b, st = O.forward(cfg, tensors, toks[9:10], states=st, first_pos=9)
-    c, _ = O.forward(cfg, tensors, toks[10:], states=st, first_pos=10)
-    assert float((torch.cat([a, b, c]) - whole).abs().max()) < 1e-9
-
-
 @pytest.mark.parametrize("name,dtype", CASES)
 @pytest.mark.parametrize("eager", [False, True])
 def test_prefill_then_token_by_token(tmp_path_factory, name, dtype, eager):
