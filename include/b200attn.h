@@ -118,6 +118,16 @@ int b200_paged_decode_attn(void* out, const void* q, const void* k_cache, const 
                            int32_t block_table_stride, float scale, void* workspace,
                            size_t workspace_bytes, int32_t num_ctas, int32_t dtype,
                            b200_stream_t stream);
+/* The same with two optional parts of the softmax: softcap > 0 turns every score s = scale q.k into
+ * softcap * tanh(s / softcap); sink (fp32 [num_heads] or NULL) adds exp(sink[h]) to the denominator of head h, an
+ * entry without key or value. softcap == 0 and sink == NULL is b200_paged_decode_attn. */
+int b200_paged_decode_attn_capped(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                  const int32_t* block_tables, const int32_t* context_lens, int32_t batch,
+                                  int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, int64_t q_stride,
+                                  int64_t out_stride, int32_t num_blocks, int32_t block_size,
+                                  int32_t block_table_stride, float scale, float softcap, const float* sink,
+                                  void* workspace, size_t workspace_bytes, int32_t num_ctas, int32_t dtype,
+                                  b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------
  * K1/K2 + K6 over an FP8 (e4m3) KV cache -- SURVEY.md 8f row f3. An EXTENSION of the path: the
@@ -189,6 +199,16 @@ int b200_prefill_varlen_attn(void* out, const void* q, const void* k, const void
                              int32_t block_table_stride, int32_t num_blocks,
                              int32_t block_size, float scale, int32_t dtype,
                              void* workspace, int64_t workspace_bytes, b200_stream_t stream);
+/* The same with a score cap and a sink as in b200_paged_decode_attn_capped; served by the tcgen05 kernel only
+ * (B200_ERR_UNSUPPORTED where that kernel cannot take the launch). */
+int b200_prefill_varlen_attn_capped(void* out, const void* q, const void* k, const void* v,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int32_t num_seqs,
+                                    int32_t total_q, int32_t total_k, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                                    int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, int64_t q_stride,
+                                    int64_t k_stride, int64_t v_stride, int64_t out_stride,
+                                    const int32_t* block_tables, int32_t block_table_stride, int32_t num_blocks,
+                                    int32_t block_size, float scale, float softcap, const float* sink, int32_t dtype,
+                                    void* workspace, int64_t workspace_bytes, b200_stream_t stream);
 
 /* Bytes of split-KV workspace that let b200_prefill_varlen_attn use every SM for ANY launch it would
  * split (few query rows against many keys): the largest such launch has 148 CTAs x 256 rows of

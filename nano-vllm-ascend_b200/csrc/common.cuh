@@ -140,6 +140,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// tanh from one ex2 and one reciprocal: 1 - 2 / (1 + e^(2x)); absolute error of a few 1e-7, exact limits at +-inf
+__device__ __forceinline__ float tanh_ex2(float x) {
+  return 1.0f - __fdividef(2.0f, 1.0f + ex2_approx(x * 2.8853900817779268f));
+}
+constexpr float kLog2e = 1.4426950408889634f;
+
 // 128-bit streaming global load / store (no L1 allocation)
 __device__ __forceinline__ uint4 ld_nc_v4(const void* ptr) {
   uint4 r;

@@ -167,7 +167,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK,
   const int unit = warp / HKV_CTA;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = p.G;
-  const float sl2 = p.scale_log2;
+  const bool capped = p.cap > 0.f;
+  const float sl2 = capped ? kLog2e : p.scale_log2;           // capped scores are already scaled
   const T* qbase = reinterpret_cast<const T*>(p.q);
   T* obase = reinterpret_cast<T*>(p.out);
 
@@ -241,6 +242,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK,
                   r3_);
           mma_16816<T>(s[0], qa[ks][0], 0u, qa[ks][1], 0u, r0_, r1_);
           mma_16816<T>(s[1], qa[ks][0], 0u, qa[ks][1], 0u, r2_, r3_);
+        }
+        if (capped) {
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) s[n][e] = p.cap * tanh_ex2(s[n][e] * p.cap_pre);
         }
         // mask tokens beyond the context (only the last tile of a sequence)
         const int valid = len - tok0;  // > 0
@@ -339,6 +346,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK,
     if (unit == 0 && g < G) {
       const bool whole = (j0 == 0) && (j1 == ntiles);
       if (whole) {
+        if (p.sink != nullptr) l_run += ex2_approx(p.sink[kv_head * G + g] * kLog2e - m_run * sl2);
         const float inv = 1.f / l_run;
         T* orow = obase + (int64_t)b * p.out_stride + (int64_t)(kv_head * G + g) * D;
 #pragma unroll
@@ -505,6 +513,21 @@ extern "C" int b200_paged_decode_attn(void* out, const void* q, const void* k_ca
                                       int32_t block_size, int32_t block_table_stride, float scale,
                                       void* workspace, size_t workspace_bytes, int32_t num_ctas,
                                       int32_t dtype, b200_stream_t stream_) {
+  return b200_paged_decode_attn_capped(out, q, k_cache, v_cache, block_tables, context_lens, batch, num_heads,
+                                       num_kv_heads, head_dim, q_stride, out_stride, num_blocks, block_size,
+                                       block_table_stride, scale, 0.f, nullptr, workspace, workspace_bytes, num_ctas,
+                                       dtype, stream_);
+}
+
+extern "C" int b200_paged_decode_attn_capped(void* out, const void* q, const void* k_cache,
+                                             const void* v_cache, const int32_t* block_tables,
+                                             const int32_t* context_lens, int32_t batch,
+                                             int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                             int64_t q_stride, int64_t out_stride, int32_t num_blocks,
+                                             int32_t block_size, int32_t block_table_stride, float scale,
+                                             float softcap, const float* sink, void* workspace,
+                                             size_t workspace_bytes, int32_t num_ctas, int32_t dtype,
+                                             b200_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   B200_RETURN_IF(dtype != B200_DTYPE_BF16 && dtype != B200_DTYPE_F16, B200_ERR_BAD_DTYPE);
   B200_RETURN_IF(batch < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_blocks <= 0 ||
@@ -563,6 +586,8 @@ extern "C" int b200_paged_decode_attn(void* out, const void* q, const void* k_ca
   p.hg_count = hg_count;
   p.rows_box = block_size < tile_tokens ? block_size : tile_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (softcap > 0.f) p.cap = softcap, p.cap_pre = scale / softcap;
+  p.sink = sink;
 
   const int chunks = num_kv_heads * head_dim / 64;
   const int chunks_box = hkv_cta * head_dim / 64;

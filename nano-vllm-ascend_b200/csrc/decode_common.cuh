@@ -25,6 +25,10 @@ struct DecodeParams {
   int hg_count;  // head groups per sequence = Hkv / HKV_CTA
   int rows_box;  // tokens per TMA op = min(block_size, TILE_TOKENS)
   float scale_log2;
+  // optional: scores capped by cap * tanh(scale * s / cap) (cap_pre = scale / cap; 0 = off), and a sink logit per
+  // query head (fp32 [H], natural-log units) that joins the softmax denominator without a value
+  float cap = 0.f, cap_pre = 0.f;
+  const float* sink = nullptr;
 };
 
 // first idx in [1, items] with prefix[idx] > t, minus one
@@ -102,6 +106,7 @@ decode_combine_kernel(const DecodeParams p, int rows /* = HKV_CTA*G */) {
         for (int i = 0; i < V; ++i) acc[i] = fmaf(s_acc[w][lane * V + i], sc, acc[i]);
       }
     }
+    if (p.sink != nullptr) l += ex2_approx(p.sink[hg * rows + r] * kLog2e - m);   // the sink joins once, after the merge
     const float inv = 1.f / l;
     T* orow = obase + (int64_t)r * D + lane * V;
 #pragma unroll

@@ -248,7 +248,7 @@ int prefill_umma_launch(void* out, const void* q, const void* k, const void* v, 
                         int64_t v_stride, int64_t out_stride, const int32_t* block_tables,
                         int bt_stride, int num_blocks, int block_size, float scale, int dtype,
                         void* workspace, int64_t workspace_bytes, int max_seqlen_k,
-                        cudaStream_t stream);  // prefill_umma.cu
+                        cudaStream_t stream, float softcap, const float* sink);  // prefill_umma.cu
 void prefill_force_query_tiles(int qt);        // prefill_umma.cu
 // B200_PREFILL_KERNEL=mma_sync forces the kernel in this file (A/B checks); default = prefill_umma.cu.
 static int prefill_kernel_choice() {
@@ -285,6 +285,23 @@ extern "C" int b200_prefill_varlen_attn(void* out, const void* q, const void* k,
                                         int32_t num_blocks, int32_t block_size, float scale,
                                         int32_t dtype, void* workspace, int64_t workspace_bytes,
                                         b200_stream_t stream) {
+  return b200_prefill_varlen_attn_capped(out, q, k, v, cu_seqlens_q, cu_seqlens_k, num_seqs, total_q, total_k,
+                                         max_seqlen_q, max_seqlen_k, num_heads, num_kv_heads, head_dim, q_stride,
+                                         k_stride, v_stride, out_stride, block_tables, block_table_stride,
+                                         num_blocks, block_size, scale, 0.f, nullptr, dtype, workspace,
+                                         workspace_bytes, stream);
+}
+
+extern "C" int b200_prefill_varlen_attn_capped(void* out, const void* q, const void* k, const void* v,
+                                               const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                               int32_t num_seqs, int32_t total_q, int32_t total_k,
+                                               int32_t max_seqlen_q, int32_t max_seqlen_k, int32_t num_heads,
+                                               int32_t num_kv_heads, int32_t head_dim, int64_t q_stride,
+                                               int64_t k_stride, int64_t v_stride, int64_t out_stride,
+                                               const int32_t* block_tables, int32_t block_table_stride,
+                                               int32_t num_blocks, int32_t block_size, float scale, float softcap,
+                                               const float* sink, int32_t dtype, void* workspace,
+                                               int64_t workspace_bytes, b200_stream_t stream) {
   B200_RETURN_IF(dtype != B200_DTYPE_BF16 && dtype != B200_DTYPE_F16, B200_ERR_BAD_DTYPE);
   B200_RETURN_IF(num_seqs < 0 || max_seqlen_q < 0 || max_seqlen_k < 0 || num_heads <= 0 ||
                      num_kv_heads <= 0,
@@ -313,9 +330,11 @@ extern "C" int b200_prefill_varlen_attn(void* out, const void* q, const void* k,
     const int rc = prefill_umma_launch(out, q, k, v, cu_seqlens_q, cu_seqlens_k, num_seqs, total_q,
         total_k, max_seqlen_q, num_heads, num_kv_heads, head_dim, q_stride, k_stride, v_stride,
         out_stride, block_tables, block_table_stride, num_blocks, block_size, scale, dtype,
-        workspace, workspace_bytes, max_seqlen_k, s);
+        workspace, workspace_bytes, max_seqlen_k, s, softcap, sink);
     if (rc != B200_ERR_UNSUPPORTED) return rc;
   }
+  // the mma.sync variant below knows neither a score cap nor a sink
+  B200_RETURN_IF(softcap > 0.f || sink != nullptr, B200_ERR_UNSUPPORTED);
   PrefillParams p;
   p.q = q, p.k = k, p.v = v, p.out = out;
   p.cu_q = cu_seqlens_q, p.cu_k = cu_seqlens_k;

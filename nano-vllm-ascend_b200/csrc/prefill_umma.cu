@@ -54,6 +54,10 @@ struct PrefillUmmaParams {
   float* part_o;     // kv_splits > 1: [total_q][H][kv_splits][D] un-normalised O
   float* part_ml;    // kv_splits > 1: [total_q][H][kv_splits][2]  (row max in the exp2 domain, row sum)
   float scale_log2;
+  // optional: scores capped by cap * tanh(scale * s / cap) (cap_pre = scale / cap; 0 = off), and a sink logit per
+  // query head (fp32 [H], natural-log units) that joins the softmax denominator without a value
+  float cap = 0.f, cap_pre = 0.f;
+  const float* sink = nullptr;
 };
 
 constexpr int kUBM = 128, kUBN = 128;
@@ -273,7 +277,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t s_addr = tb + lane_base + kSBase + t * 128;
     const uint32_t o_addr = tb + lane_base + t * 128;
-    const float sl2 = p.scale_log2;
+    const bool capped = p.cap > 0.f;
+    const float sl2 = capped ? kLog2e : p.scale_log2;   // capped scores are already scaled
     constexpr float kLazy = 8.f;                     // lazy rescale threshold (exp2 domain): O is rescaled only when the max grew by > 2^8
     float m_ref = -INFINITY, l_run = 0.f;
     for (int j = 0; j < nt; ++j) {
@@ -283,6 +288,11 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < 4; ++c) umma::ld32(s_addr + c * 32, sr[c]);
       umma::wait_ld();
+      if (capped) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          sr[c >> 5][c & 31] = __float_as_uint(p.cap * tanh_ex2(__uint_as_float(sr[c >> 5][c & 31]) * p.cap_pre));
+      }
       const int n0 = (j_lo + j) * kUBN;
       // mask (warp-uniform test: does this tile touch the diagonal or the end of the keys?)
       const int warp_row0 = m0 + t * kUBM + (warp & 3) * 32;
@@ -338,6 +348,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       l_run += sum;
     }
+    // the sink joins the denominator once: in the split that holds the first keys
+    if (p.sink != nullptr && split == 0 && nt > 0 && m_ref != -INFINITY)
+      l_run += ex2_approx(p.sink[head] * kLog2e - m_ref * sl2);
     // ---- epilogue: O / l -> global, or (split-KV) the un-normalised partial -> workspace
     if (m0 + t * kUBM < Lq) {
       T* orow = reinterpret_cast<T*>(p.out) + (int64_t)(q0 + qrow) * p.out_stride + (int64_t)head * D;
@@ -488,7 +501,7 @@ int prefill_umma_launch(void* out, const void* q, const void* k, const void* v,
                          int64_t k_stride, int64_t v_stride, int64_t out_stride,
                         const int32_t* block_tables, int bt_stride, int num_blocks, int block_size,
                         float scale, int dtype, void* workspace, int64_t workspace_bytes, int max_seqlen_k,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, float softcap, const float* sink) {
   if (q_stride % 8 != 0 || out_stride % 8 != 0 || !aligned16(out)) return B200_ERR_UNSUPPORTED;
   if (total_q <= 0) return B200_ERR_UNSUPPORTED;
   const int CH = D / 64;
@@ -500,6 +513,8 @@ int prefill_umma_launch(void* out, const void* q, const void* k, const void* v,
   p.out = out, p.out_stride = out_stride;
   p.H = H, p.G = H / Hkv, p.block_size = block_size, p.bt_stride = bt_stride;
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (softcap > 0.f) p.cap = softcap, p.cap_pre = scale / softcap;
+  p.sink = sink;
   const int qt = prefill_query_tiles(num_seqs, H, max_seqlen_q, D);
   p.kv_splits = (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0)
                     ? prefill_kv_splits(num_seqs, H, max_seqlen_q, max_seqlen_k, total_q, D, workspace_bytes, qt)

@@ -34,6 +34,10 @@ PROTOTYPES = {
                                          c_void_p, c_int32, c_int32, c_int32, c_int32, c_int64,
                                          c_int64, c_int32, c_int32, c_int32, c_float, c_void_p,
                                          c_size_t, c_int32, c_int32, c_void_p]),
+    "b200_paged_decode_attn_capped": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int32, c_int32, c_int32, c_int32, c_int64,
+                                                c_int64, c_int32, c_int32, c_int32, c_float, c_float, c_void_p,
+                                                c_void_p, c_size_t, c_int32, c_int32, c_void_p]),
     "b200_reshape_and_cache_fp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int32, c_int32, c_int32, c_int32, c_int64, c_int64,
                                              c_int32, c_int32, c_float, c_float, c_int32, c_void_p]),
@@ -46,6 +50,11 @@ PROTOTYPES = {
                                            c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                            c_int32, c_int32, c_int32, c_float, c_int32,
                                            c_void_p, c_int64, c_void_p]),
+    "b200_prefill_varlen_attn_capped": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                                  c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64,
+                                                  c_void_p, c_int32, c_int32, c_int32, c_float, c_float, c_void_p,
+                                                  c_int32, c_void_p, c_int64, c_void_p]),
     "b200_prefill_workspace_size": (c_int64, [c_int32]),
     "b200_prefill_set_query_tiles": (c_int32, [c_int32]),
     "b200_gather_dequant_fp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,

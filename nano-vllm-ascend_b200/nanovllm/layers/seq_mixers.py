@@ -156,7 +156,7 @@ class VarSizeAttention(nn.Module):
 
     def _fast(self, q) -> bool:
         rep, G = self.num_heads // self.num_kv_heads, self.num_kv_heads
-        return (not self.force_generic and not self.window and not self.softcap and self.sink is None
+        return (not self.force_generic and not self.window
                 and q.dtype in (torch.bfloat16, torch.float16) and self.dim == self.vdim
                 and self.dim in (64, 128) and rep <= 8 and (G in (1, 2, 4) or G % 8 == 0))
 
@@ -167,16 +167,22 @@ class VarSizeAttention(nn.Module):
         paged = self.k_cache.numel() > 0 and ctx.block_tables is not None
         if self._fast(q) and (paged or ctx.is_prefill):
             out = None
+            soft = dict(softcap=self.softcap, sink=self.sink)
+            # a score cap or a sink: the tcgen05 kernel only, whose TMA maps want 16-byte row strides and blocks that
+            # tile its 128-key steps
+            tma_ok = not (self.softcap or self.sink is not None) or (
+                q.stride(0) % 8 == 0 and (paged and (ctx.block_size % 128 == 0 or 128 % ctx.block_size == 0) or
+                                          not paged and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0))
             if not ctx.is_prefill:
                 out = ops.paged_decode_attn(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.context_lens,
-                                            self.scale, self.num_kv_heads, num_ctas=ctx.decode_attn_ctas)
-            elif paged and ctx.block_size % 16 == 0:
+                                            self.scale, self.num_kv_heads, num_ctas=ctx.decode_attn_ctas, **soft)
+            elif paged and ctx.block_size % 16 == 0 and tma_ok:
                 out = ops.prefill_varlen_attn(q, self.k_cache, self.v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                               ctx.max_seqlen_q, ctx.max_seqlen_k, self.scale, self.num_kv_heads,
-                                              block_tables=ctx.block_tables)
-            elif not paged:
+                                              block_tables=ctx.block_tables, **soft)
+            elif not paged and tma_ok:
                 out = ops.prefill_varlen_attn(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                              ctx.max_seqlen_k, self.scale, self.num_kv_heads)
+                                              ctx.max_seqlen_k, self.scale, self.num_kv_heads, **soft)
             if out is not None:
                 out = out.view(q.shape[0], self.num_heads * self.vdim)
                 return out if gate is None else ops.head_gate_(out, gate, self.num_heads)

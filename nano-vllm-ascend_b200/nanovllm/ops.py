@@ -123,10 +123,14 @@ def decode_workspace(batch, num_heads, num_kv_heads, head_dim, device) -> torch.
 
 
 def paged_decode_attn(q, k_cache, v_cache, block_tables, context_lens, scale, num_kv_heads,
-                      out=None, workspace=None, num_ctas=0):
-    """K6. q [B, H, D] (token-strided view allowed) -> out [B, H*D]."""
-    _need_cuda(q, k_cache, v_cache, block_tables, context_lens)
+                      out=None, workspace=None, num_ctas=0, softcap=0.0, sink=None):
+    """K6. q [B, H, D] (token-strided view allowed) -> out [B, H*D]. softcap > 0: scores become softcap *
+    tanh(score / softcap); sink fp32 [H]: exp(sink[h]) joins the softmax denominator (no key, no value)."""
+    _need_cuda(q, k_cache, v_cache, block_tables, context_lens, sink)
+    _f32(sink)
     B, H, D = q.shape
+    if sink is not None and sink.numel() != H:
+        raise ValueError("sink [H]")
     if q.stride(2) != 1 or q.stride(1) != D:
         raise ValueError("q must be contiguous in (heads, head_dim)")
     if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int32:
@@ -138,12 +142,12 @@ def paged_decode_attn(q, k_cache, v_cache, block_tables, context_lens, scale, nu
         out = torch.empty(B, H * D, dtype=q.dtype, device=q.device)
     if workspace is None:
         workspace = decode_workspace(B, H, num_kv_heads, D, q.device)
-    _C.check(_C.load().b200_paged_decode_attn(
+    _C.check(_C.load().b200_paged_decode_attn_capped(
         out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         block_tables.data_ptr(), context_lens.data_ptr(), B, H, num_kv_heads, D,
         q.stride(0) if B > 1 else H * D, out.stride(0) if B > 1 else H * D, nb, bs,
-        block_tables.stride(0), float(scale), workspace.data_ptr(), workspace.numel(),
-        int(num_ctas), _dt(q), _stream()), "b200_paged_decode_attn")
+        block_tables.stride(0), float(scale), float(softcap or 0.0), _ptr(sink), workspace.data_ptr(),
+        workspace.numel(), int(num_ctas), _dt(q), _stream()), "b200_paged_decode_attn")
     return out
 
 
@@ -213,12 +217,16 @@ def prefill_workspace(device, head_dim: int) -> torch.Tensor:
 
 
 def prefill_varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, scale,
-                        num_kv_heads, block_tables=None, out=None, workspace="auto"):
+                        num_kv_heads, block_tables=None, out=None, workspace="auto", softcap=0.0, sink=None):
     """K4/K5. q [Tq, H, D]; packed mode: k/v [Tk, Hkv, D]; paged mode (block_tables given):
     k/v are the caches [nb, bs, Hkv*D]. Returns out [Tq, H*D]. workspace: "auto" (the per-device
-    split-KV workspace), None (never split the keys across CTAs) or a uint8 CUDA tensor."""
-    _need_cuda(q, k, v, cu_seqlens_q, cu_seqlens_k, block_tables)
+    split-KV workspace), None (never split the keys across CTAs) or a uint8 CUDA tensor. softcap, sink as in
+    paged_decode_attn (the tcgen05 kernel only)."""
+    _need_cuda(q, k, v, cu_seqlens_q, cu_seqlens_k, block_tables, sink)
+    _f32(sink)
     Tq, H, D = q.shape
+    if sink is not None and sink.numel() != H:
+        raise ValueError("sink [H]")
     if q.stride(2) != 1 or q.stride(1) != D:
         raise ValueError("q must be contiguous in (heads, head_dim)")
     if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
@@ -242,12 +250,13 @@ def prefill_varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_s
     if isinstance(workspace, str):
         workspace = prefill_workspace(q.device, D)
     ws_ptr, ws_bytes = (None, 0) if workspace is None else (workspace.data_ptr(), workspace.numel())
-    _C.check(_C.load().b200_prefill_varlen_attn(
+    _C.check(_C.load().b200_prefill_varlen_attn_capped(
         out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens_q.data_ptr(),
         cu_seqlens_k.data_ptr(), num_seqs, Tq, 0 if block_tables is not None else k.shape[0],
         int(max_seqlen_q), int(max_seqlen_k), H, num_kv_heads,
         D, q.stride(0) if Tq > 1 else H * D, ks, vs, out.stride(0) if Tq > 1 else H * D, bt_ptr,
-        bt_stride, nb, bs, float(scale), _dt(q), ws_ptr, ws_bytes, _stream()), "b200_prefill_varlen_attn")
+        bt_stride, nb, bs, float(scale), float(softcap or 0.0), _ptr(sink), _dt(q), ws_ptr, ws_bytes, _stream()),
+        "b200_prefill_varlen_attn")
     return out
 
 

@@ -640,3 +640,40 @@ def test_short_convolution_tails_per_projection():
         at += n
     assert at == T
     assert float((torch.cat(outs).cpu().to(F64) - want).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("H,G,D", [(4, 2, 64), (8, 1, 128), (8, 8, 64)])
+def test_cap_and_sink_on_the_tensor_core_kernels(H, G, D):
+    """The tcgen05 prompt kernel and the paged decode kernel with a score cap and a sink against the generic kernel:
+    a long prompt, a short portion over thousands of cached keys (the keys are split over CTAs and the sink must join
+    once), and decode rows whose keys are split over CTAs beside short ones."""
+    from nanovllm import ops
+    g = torch.Generator().manual_seed(D + H)
+    n, bs, scale, cap = 4100, 64, D ** -0.5 * 2.0, 3.0
+    q = torch.randn(n, H, D, generator=g).bfloat16().cuda()
+    k = torch.randn(n, G, D, generator=g).bfloat16().cuda()
+    v = torch.randn(n, G, D, generator=g).bfloat16().cuda()
+    sink = torch.tensor([0.0, 1.5, -2.0, 0.3] * (H // 4), dtype=torch.float32).cuda()
+    nb = -(-n // bs)
+    order = torch.randperm(nb, generator=g)
+    kc = torch.zeros(nb + 1, bs, G * D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    pad = nb * bs - n
+    kc[order.cuda()] = torch.nn.functional.pad(k.view(n, -1), (0, 0, 0, pad)).view(nb, bs, -1)
+    vc[order.cuda()] = torch.nn.functional.pad(v.view(n, -1), (0, 0, 0, pad)).view(nb, bs, -1)
+    table = order.to(torch.int32).cuda()[None, :].contiguous()
+    cu = lambda *x: torch.tensor(x, dtype=torch.int32).cuda()
+    ref = ops.attn_generic(q, k, v, ops.StepSpans(cu(0, n), cu(0, n), None, n), scale, G, D, softcap=cap, sink=sink).float()
+    plain = ops.attn_generic(q[-8:], kc, vc, ops.StepSpans(cu(0, 8), cu(0, n), None, 8), scale, G, D, block_tables=table).float()
+    assert float((plain - ref[-8:]).abs().max()) > 0.05               # cap and sink matter on this input
+    got = ops.prefill_varlen_attn(q, k, v, cu(0, n), cu(0, n), n, n, scale, G, softcap=cap, sink=sink).float()
+    assert float((got - ref).abs().max()) < 3e-2
+    for ql in (128, 40):                                               # few queries, many keys: split along the keys
+        got = ops.prefill_varlen_attn(q[n - ql:], kc, vc, cu(0, ql), cu(0, n), ql, n, scale, G, block_tables=table,
+                                      softcap=cap, sink=sink).float()
+        assert float((got - ref[n - ql:]).abs().max()) < 3e-2, ql
+    rows = [n - 1, 16, 899, 0]
+    tables = table.repeat(len(rows), 1).contiguous()
+    ctx_lens = torch.tensor([r + 1 for r in rows], dtype=torch.int32).cuda()
+    got = ops.paged_decode_attn(q[rows], kc, vc, tables, ctx_lens, scale, G, softcap=cap, sink=sink).float()
+    assert float((got - ref[rows]).abs().max()) < 3e-2
