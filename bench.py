@@ -25,7 +25,8 @@ the all-reduce form and its latency, and the same workload at TP=1 (rank 0) for 
 `--hybrid` leaves the contract workload aside: the Zegopel hybrid decoder beside the dense decoder of the same width
 (prefill and decode throughput through the engine) and the rooflines of its kernels beside their like kernels;
 `--hybrid --design nirelix` does the same for the Nirelix decoder beside the Zegopel decoder of the same width, and
-`--hybrid --design fitevik` for the Fitevik decoder beside the Nirelix decoder of the same width.
+`--hybrid --design fitevik` for the Fitevik decoder beside the Nirelix decoder of the same width, and
+`--hybrid --design nurilorn` for the Nurilorn decoder beside the Zegopel decoder of the same width.
 """
 from __future__ import annotations
 
@@ -112,8 +113,9 @@ def parse_args():
     ap.add_argument("--hybrid-pairs", default=None,
                     help="model:model,... (default zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b; with --design "
                          "nirelix: nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k; with --design fitevik: "
-                         "fitevik-1k:nirelix-1k,fitevik-2k:nirelix-2k)")
-    ap.add_argument("--design", default="zegopel", choices=["zegopel", "nirelix", "fitevik"],
+                         "fitevik-1k:nirelix-1k,fitevik-2k:nirelix-2k; with --design nurilorn: "
+                         "nurilorn-1k:zegopel-1k,nurilorn-2k:zegopel-2k)")
+    ap.add_argument("--design", default="zegopel", choices=["zegopel", "nirelix", "fitevik", "nurilorn"],
                     help="with --hybrid: whose presets and kernel table are measured")
     ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8"],
                     help="fp8: e4m3 KV cache (an extra line; the contract line is the default bf16 cache)")
@@ -1030,6 +1032,140 @@ def fitevik_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
     return rows
 
 
+def nurilorn_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
+    """The kernels that the Nurilorn decoder adds or extends, alone, at the layer sizes of a `width`-wide model, as a
+    prompt step (`seqs` x tokens/seqs) and as a decode step (`seqs` rows at that context), each beside the like kernel of
+    the Zegopel (or Nirelix) decoder. frac = algorithmic bytes / time / measured copy bandwidth."""
+    from nanovllm import ops
+    from nanovllm.layers.seq_mixers import BandScaledRotary
+    dev, bf = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=g)
+    H = width // head_dim
+    G = max(1, H // 4)
+    rows = []
+
+    def add(name, step, fn, nbytes, like=None, like_fn=None, like_bytes=None, flops=None, like_flops=None):
+        t = _timed(fn, flush)
+        row = {"kernel": name, "step": step, "us": round(t * 1e6, 1), "GB/s": round(nbytes / t / 1e9),
+               "frac_of_measured_copy": round(nbytes / t / 1e9 / peak_gbs, 3)}
+        if flops:
+            row["TFLOP/s"] = round(flops / t / 1e12, 2)
+        if like_fn is not None:
+            tl = _timed(like_fn, flush)
+            row["like"] = {"kernel": like, "us": round(tl * 1e6, 1),
+                           "frac_of_measured_copy": round(like_bytes / tl / 1e9 / peak_gbs, 3)}
+            if like_flops:
+                row["like"]["TFLOP/s"] = round(like_flops / tl / 1e12, 2)
+            row["times_as_far_from_roofline_as_like"] = round((like_bytes / tl) / (nbytes / t), 2)
+            if flops and like_flops:
+                row["times_as_far_from_flop_roofline_as_like"] = round((like_flops / tl) / (flops / t), 2)
+        rows.append(row)
+
+    rot = BandScaledRotary(head_dim // 2, 1e6, True, {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+    for step, T in (("prompt", tokens), ("decode", seqs)):
+        per = T // seqs if step == "prompt" else 1
+        ctx = tokens // seqs
+        if step == "prompt":
+            cu = torch.arange(0, T + 1, per, dtype=torch.int32, device=dev)
+            spans = ops.StepSpans(cu, cu, None, per)
+        else:
+            spans = ops.StepSpans(None, None, torch.full((T,), ctx, dtype=torch.int32, device=dev))
+        # residual path: scaled branch + grouped norm (like: post-norm + add + pre-norm of the Zegopel decoder)
+        y, res = rnd(T, width).to(bf), rnd(T, width)
+        ls, w1, w2 = rnd(width), rnd(width) * 0.1, rnd(width) * 0.1
+        add("residual_scale_groupnorm", step,
+            lambda: ops.residual_scale_groupnorm_(res, y, ls, 0.5, w1, 1e-6, 4, bf), T * width * 12,
+            "residual_add_norms", lambda: ops.residual_add_norms_(y, res, w1, w2, 1e-6), T * width * 12)
+        emb = rnd(32768, width).to(bf)
+        ids = torch.randint(0, 32768, (T,), device=dev, generator=g)
+        add("residual_scale_groupnorm, embedding looked up", step,
+            lambda: ops.residual_scale_groupnorm_(res, emb, None, 32.0, w1, 1e-6, 4, bf, accumulate=False, y_index=ids),
+            T * width * 8)
+        ff = 3 * width
+        gu = rnd(T, 2 * ff).to(bf)
+        add("glu_clamped", step, lambda: ops.glu_clamped(gu, 1.702, 7.0), T * ff * 6,
+            "act_and_mul(relu)", lambda: ops.act_and_mul(gu, "relu"), T * ff * 6)
+        # mixer preparation: rotation by the step's table + value blending + scatter (like: unit norms + temperature + scatter)
+        nq, nk = H * head_dim, G * head_dim
+        C = nq + 2 * nk
+        qkv, other = rnd(T, C).to(bf), rnd(T, nk).to(bf)
+        pos = torch.arange(T, device=dev) % max(per, 1) + (0 if step == "prompt" else ctx - 1)
+        nb = (T + 15) // 16 + 1
+        kc = torch.zeros(nb, 16, nk, dtype=bf, device=dev)
+        vc = torch.zeros(nb, 16, nk, dtype=bf, device=dev)
+        sl = torch.arange(T, dtype=torch.int32, device=dev)
+        lam = torch.full((1,), 0.4, device=dev)
+        freq = rot.freq.to(dev)
+        tab = ops.rotary_table(pos, freq, rot.magnitude)
+        prep_bytes = T * (2 * (nq + nk) * 2 + nk * 2 + 2 * nk * 2)
+        add("rope_mix_cache", step,
+            lambda: ops.rope_mix_cache(qkv, tab, H, G, head_dim, head_dim, rot.dims, True, other, lam, kc, vc, sl),
+            prep_bytes + T * (nk * 2 * 2 + rot.dims * 4),
+            "unitnorm_temp_cache",
+            lambda: ops.unitnorm_temp_cache(qkv, pos, 1e-6, 0.1, 1024, H, G, head_dim, head_dim, kc, vc, sl), prep_bytes)
+        add("rotary_table (once per step)", step, lambda: ops.rotary_table(pos, freq, rot.magnitude), T * (8 + rot.dims * 4))
+        o, gl = rnd(T, nq).to(bf), rnd(T, H + 8).to(bf)
+        gfull = rnd(T, 2 * nq).to(bf)
+        add("head_gate", step, lambda: ops.head_gate_(o, gl[:, :H], H), T * nq * 4,
+            "gated_norm(gate alone)", lambda: ops.gated_norm(o, gfull[:, nq:], None, 1e-6), T * nq * 6)
+        # attention over a paged cache: the tensor-core kernels with a score cap and a sink (like: the same kernels plain,
+        # as the Zegopel decoder runs them), and the generic kernel that fp32 models run
+        bs = 64
+        per_seq = -(-ctx // bs)
+        nblk = seqs * per_seq
+        kcache, vcache = rnd(nblk + 1, bs, nk).to(bf), rnd(nblk + 1, bs, nk).to(bf)
+        tables = torch.randperm(nblk, device=dev, generator=g).to(torch.int32).view(seqs, per_seq)
+        qh = (rnd(T, H, head_dim) * 0.5).to(bf)
+        sink = torch.zeros(H, device=dev)
+        scale, cap = head_dim ** -0.5, 30.0
+        att_bytes = T * 2 * nq * 2 + seqs * ctx * 2 * nk * 2
+        if step == "prompt":
+            fl = 4.0 * seqs * (per * (per + 1) / 2) * H * head_dim
+            fast = lambda **kw: ops.prefill_varlen_attn(qh, kcache, vcache, spans.cu_q, spans.cu_k, per, per, scale, G,
+                                                        block_tables=tables, **kw)
+            name = "prefill_varlen_attn (tcgen05)"
+        else:
+            fl = 4.0 * seqs * ctx * H * head_dim
+            fast = lambda **kw: ops.paged_decode_attn(qh, kcache, vcache, tables, spans.ctx_lens, scale, G, **kw)
+            name = "paged_decode_attn"
+        add(name + ", score cap + sink", step, lambda: fast(softcap=cap, sink=sink), att_bytes,
+            name + ", plain", lambda: fast(), att_bytes, flops=fl, like_flops=fl)
+        add(name + ", sink alone", step, lambda: fast(sink=sink), att_bytes, flops=fl)
+        gt = rnd(T, H).to(bf)
+        add("attn_generic, score cap + sink + head gate", step,
+            lambda: ops.attn_generic(qh, kcache, vcache, spans, scale, G, head_dim, block_tables=tables, softcap=cap,
+                                     sink=sink, gate=gt), att_bytes,
+            "attn_generic, plain",
+            lambda: ops.attn_generic(qh, kcache, vcache, spans, scale, G, head_dim, block_tables=tables), att_bytes,
+            flops=fl, like_flops=fl)
+        # mixture of experts: the grouped softmax router and experts with the clamped unit (like: the grouped sigmoid
+        # router and silu-gated experts of the Nirelix decoder)
+        E, top, ffe = 16, 2, width // 2
+        x = rnd(T, width).to(bf)
+        logits = rnd(T, E)
+        corr = rnd(E) * 0.1
+        add("moe_route_grouped_softmax", step, lambda: ops.moe_route_grouped_softmax(logits, top, 4, 2),
+            T * (E * 4 + top * 8), "moe_route_grouped", lambda: ops.moe_route_grouped(logits, corr, top, 4, 2, 1.5),
+            T * (E * 4 + top * 8))
+        from nanovllm.layers.moe import GroupedSigmoidMoe, GroupedSoftmaxMoe
+        with torch.device(dev):
+            ours = GroupedSoftmaxMoe(width, ffe, E, top, 4, 2, glu=(1.702, 7.0)).to(bf)
+            theirs = GroupedSigmoidMoe(width, ffe, E, top, 4, 2, 1.5).to(bf)
+        for m_ in (ours, theirs):
+            for p_ in m_.parameters():
+                p_.data.copy_((torch.randn(p_.shape, device=dev, generator=g) * 0.03).to(p_.dtype))
+            m_.router.data = m_.router.data.float()
+        theirs.correction.data = theirs.correction.data.float()
+        moe_bytes = 3 * E * ffe * width * 2 + T * width * 4
+        with torch.inference_mode():
+            add("mixture of clamped-unit experts (router + experts)", step, lambda: ours(x), moe_bytes,
+                "mixture of silu-gated experts (router + experts)", lambda: theirs(x), moe_bytes,
+                flops=6.0 * T * top * ffe * width, like_flops=6.0 * T * top * ffe * width)
+    return rows
+
+
 def hybrid_compare(args):
     """--hybrid: the Zegopel presets beside the dense presets of the same width and depth, each through the engine
     (LLM.add_request / LLM.step; prompt steps, then CUDA-graph decode steps), plus the kernel table."""
@@ -1044,7 +1180,8 @@ def hybrid_compare(args):
            "config": {"batch": B, "ctx": ctx, "block_size": args.block_size, "l2": "prompts and caches exceed L2; "
                       "kernel table: 256 MB flush before every timed launch"}, "models": [], "peak_source": peak_src}
     pairs = args.hybrid_pairs or {"nirelix": "nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k",
-                                  "fitevik": "fitevik-1k:nirelix-1k,fitevik-2k:nirelix-2k"}.get(
+                                  "fitevik": "fitevik-1k:nirelix-1k,fitevik-2k:nirelix-2k",
+                                  "nurilorn": "nurilorn-1k:zegopel-1k,nurilorn-2k:zegopel-2k"}.get(
         args.design, "zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b")
     out["design"] = args.design
     for pair in pairs.split(","):
@@ -1066,7 +1203,8 @@ def hybrid_compare(args):
             release(llm)
             del llm
             torch.cuda.empty_cache()
-    table = {"nirelix": nirelix_kernel_table, "fitevik": fitevik_kernel_table}.get(args.design, hybrid_kernel_table)
+    table = {"nirelix": nirelix_kernel_table, "fitevik": fitevik_kernel_table,
+             "nurilorn": nurilorn_kernel_table}.get(args.design, hybrid_kernel_table)
     out["kernels"] = {"width_1024_head_128": table(1024, 128, 16384, 16, peak),
                       "width_2048_head_64": table(2048, 64, 16384, 16, peak)}
     out["clocks"] = clocks.stop()

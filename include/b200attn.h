@@ -319,6 +319,13 @@ int b200_moe_gemm_gate_up(void* h, const void* x, const void* w13, const int32_t
                           const int32_t* sorted_pair, int32_t hidden, int32_t inter,
                           int32_t num_local, int32_t top_k, int64_t x_stride, int32_t dtype,
                           b200_stream_t stream);
+/* b200_moe_gemm_gate_up with the clamped unit in its epilogue: h = g sigmoid(alpha g) (u + 1) with g = min(x Wg^T,
+ * limit), u = clamp(x Wu^T, -limit, limit), limit > 0. */
+int b200_moe_gemm_gate_up_glu(void* h, const void* x, const void* w13, const int32_t* offsets,
+                              const int32_t* sorted_pair, int32_t hidden, int32_t inter, int32_t num_local,
+                              int32_t top_k, int64_t x_stride, float alpha, float limit, int32_t dtype,
+                              b200_stream_t stream);
+
 /* Experts without a gate: h[pos, :inter] = act(x[sorted_pair[pos] / top_k] . w1[e]^T in dtype), w1 [num_local, inter,
  * hidden]; act as in b200_act_only; hidden % 64 == 0, inter % 128 == 0. */
 int b200_moe_gemm_up_act(void* h, const void* x, const void* w1, const int32_t* offsets,

@@ -176,6 +176,8 @@ struct MoeGemmParams {
   int64_t a_stride;            // elements between rows of a
   int K, n_out, top_k;
   int act;                     // up alone (mode 2): 0 silu, 1 relu, 2 gelu (tanh form), 3 squared relu
+  float glu_alpha, glu_limit;  // gate_up with glu_limit > 0: the clamped unit g sigmoid(alpha g) (u + 1), g = min(gate,
+                               // limit), u = clamp(up, +-limit), in place of silu(gate) * up
 };
 
 constexpr int kMoeStages = 4;
@@ -304,7 +306,17 @@ __device__ __forceinline__ void moe_gemm_pass(const MoeGemmParams& p, uint8_t* s
         // gate_up in the model dtype (F.linear), silu in fp32 -> dtype, dtype multiply with `up`
         const float g0 = to_f32<T>(from_f32<T>(acc[mf][0][2 * r])), g1 = to_f32<T>(from_f32<T>(acc[mf][0][2 * r + 1]));
         const float u0 = to_f32<T>(from_f32<T>(acc[mf][1][2 * r])), u1 = to_f32<T>(from_f32<T>(acc[mf][1][2 * r + 1]));
-        const uint32_t h = pack2<T>(__fmul_rn(silu_round<T>(g0), u0), __fmul_rn(silu_round<T>(g1), u1));
+        uint32_t h;
+        if (p.glu_limit > 0.f) {
+          // the clamped unit on the projections as the model dtype holds them, fp32 arithmetic, one rounding
+          const float L = p.glu_limit;
+          const float c0 = fminf(g0, L), c1 = fminf(g1, L);
+          const float v0 = fminf(fmaxf(u0, -L), L) + 1.0f, v1 = fminf(fmaxf(u1, -L), L) + 1.0f;
+          h = pack2<T>(__fdividef(c0, 1.0f + __expf(-p.glu_alpha * c0)) * v0,
+                       __fdividef(c1, 1.0f + __expf(-p.glu_alpha * c1)) * v1);
+        } else {
+          h = pack2<T>(__fmul_rn(silu_round<T>(g0), u0), __fmul_rn(silu_round<T>(g1), u1));
+        }
         *reinterpret_cast<uint32_t*>(og + pos * p.n_out + n0 + warp * 8 + 2 * t4) = h;
       } else if (kMode == 2) {
         // up in the model dtype (F.linear), the activation in fp32 -> dtype
@@ -484,6 +496,19 @@ extern "C" int b200_moe_gemm_gate_up(void* h, const void* x, const void* w13, co
                                 x_stride, dtype);
   if (rc != B200_OK) return rc;
   MoeGemmParams p{x, w13, h, offsets, sorted_pair, nullptr, x_stride, hidden, inter, top_k, 0};
+  return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(1, p, num_local, (cudaStream_t)stream)
+                                  : moe_gemm_launch<__half>(1, p, num_local, (cudaStream_t)stream);
+}
+
+extern "C" int b200_moe_gemm_gate_up_glu(void* h, const void* x, const void* w13, const int32_t* offsets,
+                                         const int32_t* sorted_pair, int32_t hidden, int32_t inter,
+                                         int32_t num_local, int32_t top_k, int64_t x_stride, float alpha,
+                                         float limit, int32_t dtype, b200_stream_t stream) {
+  const int rc = moe_gemm_check(x, w13, h, offsets, sorted_pair, hidden, inter, 64, num_local, top_k,
+                                x_stride, dtype);
+  if (rc != B200_OK) return rc;
+  B200_RETURN_IF(!(limit > 0.f), B200_ERR_BAD_SHAPE);
+  MoeGemmParams p{x, w13, h, offsets, sorted_pair, nullptr, x_stride, hidden, inter, top_k, 0, alpha, limit};
   return dtype == B200_DTYPE_BF16 ? moe_gemm_launch<__nv_bfloat16>(1, p, num_local, (cudaStream_t)stream)
                                   : moe_gemm_launch<__half>(1, p, num_local, (cudaStream_t)stream);
 }

@@ -1040,6 +1040,60 @@ rope_mix_cache_kernel(T* __restrict__ qkv, int64_t stride, const float2* __restr
     for (int i = dims + lane; i < dim; i += 32) dst[i] = x[i];
 }
 
+// 16-byte form of rope_mix_cache (neighbouring pairs; dim, vdim, dims multiples of 8; 16-byte aligned rows): one thread
+// per 8 consecutive columns of a token's row, which lie in one head and either inside or outside its rotated part.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_mix_cache_vec_kernel(T* __restrict__ qkv, int64_t stride, const float2* __restrict__ table, int dims,
+                          const T* __restrict__ v_other, int64_t v_other_stride, const float* __restrict__ lambda,
+                          T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
+                          int slot_pairs, int block_size, int num_tokens, int H, int G, int dim, int vdim) {
+  pdl_wait();
+  const int nq = H * dim, nk = G * dim, nv = G * vdim;
+  const int vecs = (nq + nk + nv) / 8;
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (int64_t)num_tokens * vecs) return;
+  const int t = (int)(e / vecs), c = (int)(e % vecs) * 8;
+  T* x = qkv + (int64_t)t * stride + c;
+  int64_t slot = -1;
+  if (k_cache != nullptr && c >= nq)
+    slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+  float f[8];
+  if (c >= nq + nk) {                                // a value vector
+    const int cv = c - nq - nk;
+    if (v_other == nullptr && slot < 0) return;
+    load8<T>(x, f);
+    if (v_other != nullptr) {
+      float o[8];
+      load8<T>(v_other + (int64_t)t * v_other_stride + cv, o);
+      const float lam = *lambda;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = (1.0f - lam) * f[i] + lam * o[i];
+      store8<T>(x, f);
+      load8<T>(x, f);                                // what is cached is exactly what the row now holds
+    }
+    if (slot >= 0) store8<T>(v_cache + slot * (int64_t)nv + cv, f);
+    return;
+  }
+  const int within = c % dim;                        // q heads then k heads, both `dim` wide
+  if (within >= dims && slot < 0) return;            // passes unchanged and is not cached
+  load8<T>(x, f);
+  if (within < dims) {
+    const float4* cs = reinterpret_cast<const float4*>(table + (int64_t)t * (dims / 2) + within / 2);
+    const float4 a = cs[0], b = cs[1];               // (cos, sin) of four neighbouring pairs
+    const float co[4] = {a.x, a.z, b.x, b.z}, si[4] = {a.y, a.w, b.y, b.w};
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r[2 * i] = f[2 * i] * co[i] - f[2 * i + 1] * si[i];
+      r[2 * i + 1] = f[2 * i + 1] * co[i] + f[2 * i] * si[i];
+    }
+    store8<T>(x, r);
+    load8<T>(x, f);
+  }
+  if (slot >= 0 && c >= nq) store8<T>(k_cache + slot * (int64_t)nk + (c - nq), f);
+}
+
 // out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]): one logit per (token, head). In place when out == x.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -1052,6 +1106,23 @@ head_gate_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restri
   const int64_t t = th / H;
   const int hd = (int)(th % H);
   out[e] = from_f32<T>(to_f32<T>(x[e]) * sigmoid_f(to_f32<T>(gate[t * gate_stride + hd])));
+}
+
+// 16-byte form (vdim % 8 == 0): one thread per 8 consecutive columns, which lie in one head
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_vec_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ gate, int64_t gate_stride,
+                     int64_t vecs, int H, int vdim) {
+  pdl_wait();
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= vecs) return;
+  const int64_t th = e * 8 / vdim;
+  const float s = sigmoid_f(to_f32<T>(gate[(th / H) * gate_stride + (int)(th % H)]));
+  float f[8];
+  load8<T>(x + e * 8, f);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] *= s;
+  store8<T>(out + e * 8, f);
 }
 
 }  // namespace b200
@@ -1387,6 +1458,16 @@ extern "C" int b200_rope_mix_cache(void* qkv, int64_t stride, const float* table
   B200_RETURN_IF(!qkv || (dims > 0 && !table) || (k_cache == nullptr) != (v_cache == nullptr) || (k_cache && !slots) ||
                      (v_other && !lambda),
                  B200_ERR_NULL_POINTER);
+  if (interleaved && dim % 8 == 0 && vdim % 8 == 0 && dims % 8 == 0 && stride % 8 == 0 && aligned16(qkv) &&
+      (!v_other || (aligned16(v_other) && v_other_stride % 8 == 0)) &&
+      (!k_cache || (aligned16(k_cache) && aligned16(v_cache))) && (dims == 0 || aligned16(table))) {
+    const int64_t total = (int64_t)num_tokens * ((num_heads * dim + num_kv_heads * (dim + vdim)) / 8);
+    B200_DISPATCH_3(dtype, T, launch_pdl(rope_mix_cache_vec_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256),
+                                         0, (cudaStream_t)stream, (T*)qkv, stride, (const float2*)table, dims,
+                                         (const T*)v_other, v_other_stride, lambda, (T*)k_cache, (T*)v_cache, slots,
+                                         slot_pairs, block_size, num_tokens, num_heads, num_kv_heads, dim, vdim));
+    return finish_launch();
+  }
   const int64_t units = (int64_t)num_tokens * (num_heads + 2 * num_kv_heads);
   const dim3 grid((unsigned)((units + 7) / 8));
   B200_DISPATCH_3(dtype, T, launch_pdl(rope_mix_cache_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)qkv,
@@ -1402,6 +1483,12 @@ extern "C" int b200_head_gate(void* out, const void* x, const void* gate, int64_
   if (rows == 0) return B200_OK;
   B200_RETURN_IF(!out || !x || !gate, B200_ERR_NULL_POINTER);
   const int64_t total = (int64_t)rows * num_heads * vdim;
+  if (vdim % 8 == 0 && aligned16(out) && aligned16(x)) {
+    B200_DISPATCH_3(dtype, T, launch_pdl(head_gate_vec_kernel<T>, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0,
+                                         (cudaStream_t)stream, (T*)out, (const T*)x, (const T*)gate, gate_stride,
+                                         total / 8, num_heads, vdim));
+    return finish_launch();
+  }
   B200_DISPATCH_3(dtype, T, launch_pdl(head_gate_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
                                        (cudaStream_t)stream, (T*)out, (const T*)x, (const T*)gate, gate_stride, total,
                                        num_heads, vdim));

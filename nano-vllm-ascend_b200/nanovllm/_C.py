@@ -77,6 +77,8 @@ PROTOTYPES = {
                                  c_int32, c_void_p]),
     "b200_moe_gemm_gate_up": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                         c_int32, c_int32, c_int32, c_int64, c_int32, c_void_p]),
+    "b200_moe_gemm_gate_up_glu": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                            c_int32, c_int32, c_int32, c_int64, c_float, c_float, c_int32, c_void_p]),
     "b200_moe_gemm_up_act": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                        c_int32, c_int64, c_int32, c_int32, c_void_p]),
     "b200_moe_gemm_down": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -145,9 +145,10 @@ class GroupedSoftmaxMoe(nn.Module):
     groups of neighbours of which only the ``keep`` best (by their largest s) stay in play, ``top_k`` experts are chosen
     and weighted by s / (sum of the chosen s + 1e-20). Experts are gate/up/down MLPs without biases, stacked in two
     tensors; ``glu = (alpha, limit)`` selects the clamped unit g sigmoid(alpha g) (u + 1) with g = min(gate, limit),
-    u = clamp(up, +-limit) in place of silu(g) u. Prompt-sized batches of 16-bit models whose sizes fit run both products
-    on the grouped tcgen05 GEMM of csrc/moe_umma.cu with the unit between them; everything else (fp32, other sizes,
-    decode-sized batches) on the generic kernels of csrc/moe_generic.cu with fp32 routing weights."""
+    u = clamp(up, +-limit) in place of silu(g) u. 16-bit models whose sizes fit run the expert GEMMs on the tensor-core
+    kernels (the grouped tcgen05 GEMM of csrc/moe_umma.cu for prompt-sized batches, the weight-streaming kernels of
+    csrc/moe.cu below that); everything else (fp32, other sizes) on the generic kernels of csrc/moe_generic.cu with
+    fp32 routing weights."""
 
     def __init__(self, hidden_size: int, inter: int, num_experts: int, top_k: int, groups: int = 1, keep: int = 1,
                  glu: tuple[float, float] | None = None):
@@ -175,8 +176,7 @@ class GroupedSoftmaxMoe(nn.Module):
                 and self.top_k <= 8 and self.num_experts <= 256):
             if self.glu is None:
                 return ops.moe_experts(x, self.w13, self.w2, ids, w.to(x.dtype), plan)
-            if x.shape[0] * self.top_k >= ops._MOE_BIG_GEMM_ROWS * self.num_experts:
-                return ops.moe_experts_glu_clamped(x, self.w13, self.w2, ids, w.to(x.dtype), plan, *self.glu)
+            return ops.moe_experts_glu_clamped(x, self.w13, self.w2, ids, w.to(x.dtype), plan, *self.glu)
         return ops.moe_experts_generic(x, self.w13, self.w2, w, plan, glu=self.glu)
 
 

@@ -599,10 +599,11 @@ def moe_experts_ungated(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, top
 
 def moe_experts_glu_clamped(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_ids: torch.Tensor,
                             topk_weights: torch.Tensor, plan: MoePlan, alpha: float, limit: float) -> torch.Tensor:
-    """Gated experts whose unit is the clamped one of glu_clamped, prompt-sized batches of 16-bit models on the grouped
-    tcgen05 GEMM: rows gathered by expert, gate and up rows of every expert as ONE product (w13 [E, 2*inter, hidden]),
-    the unit, the down product with the routing weights in its epilogue, the per-token combine. topk_weights [T, k] in
-    x's dtype. hidden % 128 == 0, inter % 64 == 0."""
+    """Gated experts whose unit is the clamped one of glu_clamped, 16-bit models on the tensor-core kernels. Prompt-sized
+    batches run on the grouped tcgen05 GEMM: rows gathered by expert, gate and up rows of every expert as ONE product
+    (w13 [E, 2*inter, hidden]), the unit, the down product with the routing weights in its epilogue; smaller ones on the
+    weight-streaming kernels (the unit is the gate/up product's epilogue). Then the per-token combine. topk_weights
+    [T, k] in x's dtype. hidden % 128 == 0, inter % 64 == 0."""
     _need_cuda(x, w13, w2, topk_ids, topk_weights)
     T, hidden = x.shape
     E, two_i, h2 = w13.shape
@@ -616,9 +617,19 @@ def moe_experts_glu_clamped(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor
     k = plan.top_k
     pairs = T * k
     lib = _C.load()
+    y = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
+    if _MOE_BIG_GEMM == "stream" or pairs < _MOE_BIG_GEMM_ROWS * E:
+        h = torch.empty(pairs, inter, dtype=x.dtype, device=x.device)
+        _C.check(lib.b200_moe_gemm_gate_up_glu(h.data_ptr(), x.data_ptr(), w13.data_ptr(), plan.offsets.data_ptr(),
+                                               plan.sorted_pair.data_ptr(), hidden, inter, E, k,
+                                               x.stride(0) if T > 1 else hidden, float(alpha), float(limit), _dt(x),
+                                               _stream()), "b200_moe_gemm_gate_up_glu")
+        _C.check(lib.b200_moe_gemm_down(y.data_ptr(), h.data_ptr(), w2.data_ptr(), plan.offsets.data_ptr(),
+                                        plan.sorted_pair.data_ptr(), topk_weights.data_ptr(), inter, hidden, E, k,
+                                        _dt(x), _stream()), "b200_moe_gemm_down")
+        return _moe_combine(lib, y, topk_ids, plan, T, hidden, None, x)
     xs = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
     gu = torch.empty(pairs, two_i, dtype=x.dtype, device=x.device)
-    y = torch.empty(pairs, hidden, dtype=x.dtype, device=x.device)
     _C.check(lib.b200_moe_gather_rows(xs.data_ptr(), x.data_ptr(), plan.offsets.data_ptr(), plan.sorted_pair.data_ptr(),
                                       pairs, E, k, hidden, x.stride(0) if T > 1 else hidden, _dt(x), _stream()),
              "b200_moe_gather_rows")

@@ -349,7 +349,7 @@ def test_band_scaled_rotation(scaling, dims, dim):
     f, mag = O.yarn_frequencies(r)
     br = BandScaledRotary(dims, 1e4, True, r.get("scaling"))
     assert float((br.freq - f).abs().max()) < 1e-15 and abs(br.magnitude - mag) < 1e-15
-    H, G, dv, T = 3, 1, 4, 7
+    H, G, dv, T = 3, 1, 8, 7                                           # dims 6 / dim 10 takes the scalar form, the others 16 bytes
     g = torch.Generator().manual_seed(dims)
     pos = torch.tensor([0, 1, 2, 63, 64, 4097, 1000003])
     qkv = torch.randn(T, H * dim + G * dim + G * dv, generator=g, dtype=F64)
@@ -365,14 +365,16 @@ def test_band_scaled_rotation(scaling, dims, dim):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_value_blending_and_cache_rows(dtype):
+@pytest.mark.parametrize("dv,skip", [(12, 5), (16, 8)])
+def test_value_blending_and_cache_rows(dtype, dv, skip):
     """v <- (1 - lambda) v + lambda v_other in place, rotated k and blended v at their slots (flat, and (block, offset)
-    pairs; a negative slot writes nothing); a layer that does not blend stores its values as they are."""
+    pairs; a negative slot writes nothing); a layer that does not blend stores its values as they are. Value size 12
+    behind an unaligned view takes the scalar form, 16 behind an aligned one the 16-byte form."""
     from nanovllm import ops
-    H, G, d, dv, T, bs = 4, 2, 16, 12, 6, 4
+    H, G, d, T, bs = 4, 2, 16, 6, 4
     g = torch.Generator().manual_seed(1)
     qkv = torch.randn(T, (H + G) * d + G * dv, generator=g, dtype=F64).to(dtype)
-    other = torch.randn(T, G * dv + 5, generator=g, dtype=F64).to(dtype)[:, 5:]                # a row-strided view
+    other = torch.randn(T, G * dv + skip, generator=g, dtype=F64).to(dtype)[:, skip:]          # a row-strided view
     lam = torch.tensor([0.3], dtype=torch.float32)
     pos = torch.arange(10, 10 + T)
     r = rot(8, 100.0)
