@@ -84,8 +84,18 @@ def config_c():
                        layer(4, 2, 64, 64, r, conv=4, scale=0.125, softcap=20.0, mlp=moe(8, 2, 128, 4, 2))]}
 
 
-CONFIGS = {"a": config_a, "b": config_b, "c": config_c}
-STRICT_BF16 = {"a": False, "b": True, "c": False}
+def config_d():
+    """Nothing is a multiple of 8: width 100 in five norm groups, five heads of 10 (6 rotated) with values of 6, 50- and
+    18-wide feed-forwards, three experts of which one is chosen, 135 projection columns per token."""
+    r = rot(6, 777.0, (3.0, 20, 4.0, 0.5))
+    return {"architecture": "Nurilorn", "vocab": 97, "width": 100, "norm": {"eps": 1e-4, "groups": 5},
+            "embedding": {"scale": 3.0}, "residual_mult": 0.8, "logit_scale": 1.5,
+            "layers": [layer(5, 5, 10, 6, r, conv=3, scale=0.4, softcap=5.0, mlp=dense(50)),
+                       layer(5, 5, 10, 6, r, conv=3, scale=0.4, softcap=5.0, mlp=moe(3, 1, 18))]}
+
+
+CONFIGS = {"a": config_a, "b": config_b, "c": config_c, "d": config_d}
+STRICT_BF16 = {"a": False, "b": True, "c": False, "d": False}
 _MODELS = {}
 
 
@@ -152,7 +162,8 @@ def feed(eng, rid, toks, cuts):
     return torch.cat(outs)
 
 
-CASES = [("a", "float32"), ("a", "bfloat16"), ("b", "float32"), ("b", "bfloat16"), ("c", "float32"), ("c", "bfloat16")]
+CASES = [("a", "float32"), ("a", "bfloat16"), ("b", "float32"), ("b", "bfloat16"), ("c", "float32"), ("c", "bfloat16"),
+         ("d", "float32"), ("d", "bfloat16")]
 
 
 # ------------------------------------------------------------------ whole prompts, decoding, portions

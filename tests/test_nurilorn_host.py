@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import nurilorn_oracle as O
-from test_nurilorn_gpu import config_a, config_b, config_c, layer, rot, tokens_of
+from test_nurilorn_gpu import config_a, config_b, config_c, config_d, layer, rot, tokens_of
 
 F64 = torch.float64
 
@@ -32,7 +32,7 @@ def test_registry_native_config_and_presets(tmp_path):
     assert all(e["mixer"]["heads"] % e["mixer"]["kv_heads"] == 0 for e in big["layers"])
 
 
-@pytest.mark.parametrize("make", [config_a, config_b, config_c])
+@pytest.mark.parametrize("make", [config_a, config_b, config_c, config_d])
 def test_checkpoint_tensors_route_onto_the_model(tmp_path, make):
     """Every tensor of a checkpoint lands somewhere, every parameter is covered, the fused projection holds q, k, v and
     the gate rows in the order the mixer slices them, experts are stacked gate rows first."""
