@@ -110,18 +110,20 @@ def test_band_scaled_frequencies():
     """Fast pairs keep their frequency, slow ones are divided by the factor, the ramp lies between; the magnitude grows
     with the logarithm of the factor; without a stretch nothing changes."""
     from nanovllm.layers.seq_mixers import BandScaledRotary
-    plain = BandScaledRotary(32, 1e6, True, None)
+    plain = BandScaledRotary(48, 5e5, True, None)
     assert plain.magnitude == 1.0 and float(plain.freq[0]) == 1.0
-    assert float(plain.freq[5]) == pytest.approx(1e6 ** (-10 / 32))
-    sc = {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}
-    br = BandScaledRotary(32, 1e6, True, sc)
-    f, mag = O.yarn_frequencies({"dims": 32, "base": 1e6, "scaling": sc})
-    assert torch.equal(br.freq, f) and br.magnitude == mag == pytest.approx(0.1 * math.log(4.0) + 1)
+    assert float(plain.freq[5]) == pytest.approx(5e5 ** (-10 / 48))
+    sc = {"factor": 6.0, "original": 2048, "fast": 24.0, "slow": 2.0}
+    br = BandScaledRotary(48, 5e5, True, sc)
+    f, mag = O.yarn_frequencies({"dims": 48, "base": 5e5, "scaling": sc})
+    assert torch.equal(br.freq, f) and br.magnitude == mag == pytest.approx(0.1 * math.log(6.0) + 1)
     ratio = br.freq / plain.freq
-    assert float(ratio[0]) == 1.0 and float(ratio[-1]) == 0.25
+    assert float(ratio[0]) == 1.0 and float(ratio[-1]) == pytest.approx(1 / 6.0)
     assert bool((ratio[1:] <= ratio[:-1] + 1e-15).all())               # monotone from 1 down to 1 / factor
-    assert 0 < int((ratio == 1.0).sum()) < 16 and 0 < int((ratio == 0.25).sum()) < 16
-    assert br.key != plain.key and BandScaledRotary(32, 1e6, True, dict(sc)).key == br.key
+    # pairs 0..4 turn at least 24 times over the original length and keep their frequency, pairs from 10 on turn at
+    # most twice and are divided by the factor, the ramp lies between
+    assert int((ratio == 1.0).sum()) == 5 and int(((ratio - 1 / 6.0).abs() < 1e-15).sum()) == 14
+    assert br.key != plain.key and BandScaledRotary(48, 5e5, True, dict(sc)).key == br.key
 
 
 # ------------------------------------------------------------------ the oracle's own invariants
